@@ -47,6 +47,9 @@ class ScheduleEntry:
 
     layer: int
     cache_of: Optional[int] = None
+    # the number of the pass (of a stretch of layers that runs several times) that begins at this stop: the model's
+    # ``reentry`` part runs on the residual stream before the stop's layer
+    enters: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -65,9 +68,13 @@ class ModelSpec:
     ignored_prefixes: Tuple[str, ...] = ()
     # names that are never prefixed (e.g. the output head of the whole checkpoint)
     unprefixed_names: Tuple[str, ...] = ()
+    # run on the residual stream at the stops that say ``enters`` (None: the model has no such stops)
+    reentry: Optional[PartSpec] = None
 
     def validate(self) -> None:
         for i, stop in enumerate(self.schedule):
+            if stop.enters is not None and self.reentry is None:
+                raise ValueError(f"schedule[{i}] begins pass {stop.enters}, but the model has no reentry part")
             if not 0 <= stop.layer < len(self.layers):
                 raise ValueError(f"schedule[{i}] names layer {stop.layer}, model has {len(self.layers)}")
             if stop.cache_of is not None:

@@ -17,6 +17,7 @@
 // kept tokens that the window has left behind, then the window; scores, bias and softmax in float.
 // The order of every sum depends on the query's position alone.
 #include "common.cuh"
+#include "rotary.cuh"
 
 #define BATT_WARPS 4
 #define BATT_MAX_D 512
@@ -27,7 +28,7 @@ __global__ void biased_attention_generic_kernel(
     const T* __restrict__ vpages, const int* __restrict__ block_table, int table_width,
     const int* __restrict__ token_seq, const int* __restrict__ cu_q, const int* __restrict__ q_start_pos,
     int n_tokens, int nq, int nkv, int dk, int dv, int page_size, int window, int keep_first, float scale,
-    const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ sink, int v_row) {
+    const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ sink, int v_row, float softcap) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ __align__(16) unsigned char att_smem[];
@@ -75,6 +76,7 @@ __global__ void biased_attention_generic_kernel(
         float dot = 0.f;
         for (int c = 0; c < dk; ++c) dot = fmaf(qs[c], to_f32(kr[c]), dot);
         s = dot * scale;
+        if (softcap > 0.f) s = softcap * tanhf(s / softcap);      // the scaled score squashed into (-cap, cap)
         if (r1) s -= b1 * log1pf(b2 * (float)(p - key));
       }
       const float m_new = fmaxf(m, warp_max(s));  // finite: every tile holds at least one valid key
@@ -144,7 +146,7 @@ static int biased_attention_generic(const void* qkv, int qkv_stride, void* out, 
                                     const int* block_table, int table_width, const int* token_seq, const int* cu_q,
                                     const int* q_start_pos, int n_tokens, int nq, int nkv, int dk, int dv, int page_size,
                                     int window, int keep_first, float scale, const float* r1, const float* r2, const float* sink,
-                                    int v_row, void* stream) {
+                                    int v_row, float softcap, void* stream) {
   if (n_tokens <= 0) return 0;
   if (v_row <= 0) v_row = dv;
   if (dk <= 0 || dv <= 0 || dv > BATT_MAX_D || dk > 4096 || nkv <= 0 || nq % nkv || window < 0 || keep_first < 0)
@@ -158,7 +160,7 @@ static int biased_attention_generic(const void* qkv, int qkv_stride, void* out, 
   }
   launch(biased_attention_generic_kernel<T>, dim3(blocks), dim3(BATT_WARPS * 32), smem, (cudaStream_t)stream, (const T*)qkv,
          qkv_stride, (T*)out, (const T*)kpages, (const T*)vpages, block_table, table_width, token_seq, cu_q, q_start_pos, n_tokens,
-         nq, nkv, dk, dv, page_size, window, keep_first, scale, r1, r2, sink, v_row);
+         nq, nkv, dk, dv, page_size, window, keep_first, scale, r1, r2, sink, v_row, softcap);
   return launch_status();
 }
 
@@ -173,13 +175,13 @@ static int kv_store_mix(void* qkv, int qkv_stride, const void* v_other, int ld_o
 
 Q25_EXPORT int q25_biased_attention_generic_f32(const void* qkv, int qs, void* out, const void* kp, const void* vp, const int* bt,
         int tw, const int* ts, const int* cu, const int* sp, int n, int nq, int nkv, int dk, int dv, int ps, int window, int keep, float scale,
-        const float* r1, const float* r2, const float* sink, int v_row, void* s) {
-  return biased_attention_generic<float>(qkv, qs, out, kp, vp, bt, tw, ts, cu, sp, n, nq, nkv, dk, dv, ps, window, keep, scale, r1, r2, sink, v_row, s);
+        const float* r1, const float* r2, const float* sink, int v_row, float softcap, void* s) {
+  return biased_attention_generic<float>(qkv, qs, out, kp, vp, bt, tw, ts, cu, sp, n, nq, nkv, dk, dv, ps, window, keep, scale, r1, r2, sink, v_row, softcap, s);
 }
 Q25_EXPORT int q25_biased_attention_generic_bf16(const void* qkv, int qs, void* out, const void* kp, const void* vp, const int* bt,
         int tw, const int* ts, const int* cu, const int* sp, int n, int nq, int nkv, int dk, int dv, int ps, int window, int keep, float scale,
-        const float* r1, const float* r2, const float* sink, int v_row, void* s) {
-  return biased_attention_generic<bf16>(qkv, qs, out, kp, vp, bt, tw, ts, cu, sp, n, nq, nkv, dk, dv, ps, window, keep, scale, r1, r2, sink, v_row, s);
+        const float* r1, const float* r2, const float* sink, int v_row, float softcap, void* s) {
+  return biased_attention_generic<bf16>(qkv, qs, out, kp, vp, bt, tw, ts, cu, sp, n, nq, nkv, dk, dv, ps, window, keep, scale, r1, r2, sink, v_row, softcap, s);
 }
 Q25_EXPORT int q25_kv_store_mix_f32(void* qkv, int qs, const void* vo, int ldo, float mix, void* kp, void* vp, const int* slot, int n,
                                     int nq, int nkv, int dk, int dv, int ps, void* s) {
@@ -188,6 +190,74 @@ Q25_EXPORT int q25_kv_store_mix_f32(void* qkv, int qs, const void* vo, int ldo, 
 Q25_EXPORT int q25_kv_store_mix_bf16(void* qkv, int qs, const void* vo, int ldo, float mix, void* kp, void* vp, const int* slot, int n,
                                      int nq, int nkv, int dk, int dv, int ps, void* s) {
   return kv_store_mix<bf16>(qkv, qs, vo, ldo, mix, kp, vp, slot, n, nq, nkv, dk, dv, ps, s);
+}
+
+// Queries and keys unit-normed per head and turned, keys kept as values: one block per token, a warp per head.
+// Row of the token: [nq query heads | nkv key heads], dk channels each.  Every head is divided by its root mean
+// square (eps inside the root) and multiplied by wq / wk (dk numbers shared by the heads; nullptr: heads are
+// left as projected); its first 2 * half channels are then turned by the token's angles.  Queries are written
+// back in place.  Keys go to their page slot turned; with keys_as_values the key as projected (before norm and
+// rotation) is the token's value and goes to the value pages.  Statistics, weights and angles in float.
+template <typename T>
+__global__ void qk_norm_store_kernel(T* __restrict__ qk, int qk_stride, const float* __restrict__ wq, const float* __restrict__ wk,
+                                     float eps, const float* __restrict__ angles, int half, int layout, T* __restrict__ kpages,
+                                     T* __restrict__ vpages, const int* __restrict__ kv_slot, int nq, int nkv, int dk, int page_size,
+                                     int keys_as_values) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ __align__(16) float qkn_smem[];        // a row of dk floats per warp
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  float* vals = qkn_smem + warp * dk;
+  const int n = blockIdx.x;
+  const int slot = kv_slot ? kv_slot[n] : -1;
+  const int page = slot / page_size, in_page = slot % page_size;
+  const float* ang = half > 0 ? angles + (size_t)n * half * 2 : nullptr;
+  for (int head = warp; head < nq + nkv; head += n_warps) {
+    T* row = qk + (size_t)n * qk_stride + (size_t)head * dk;
+    const bool is_key = head >= nq;
+    const float* w = is_key ? wk : wq;
+    const size_t page_row = is_key ? ((size_t)page * nkv + (head - nq)) * page_size + in_page : 0;
+    float sq = 0.f;
+    for (int c = lane; c < dk; c += 32) {
+      const float v = to_f32(row[c]);
+      if (is_key && keys_as_values && slot >= 0) vpages[page_row * dk + c] = row[c];
+      sq = fmaf(v, v, sq);
+      vals[c] = v;
+    }
+    sq = warp_sum(sq);
+    if (w) {
+      const float inv = 1.0f / sqrtf(sq / (float)dk + eps);
+      for (int c = lane; c < dk; c += 32) vals[c] = vals[c] * inv * w[c];
+    }
+    __syncwarp();
+    for (int c = lane; c < dk; c += 32) {
+      const T v = from_f32<T>(rotary_channel<float>(vals, c, half, layout, ang));
+      if (is_key) { if (slot >= 0) kpages[page_row * dk + c] = v; }
+      else row[c] = v;
+    }
+    __syncwarp();
+  }
+}
+
+template <typename T>
+static int qk_norm_store(void* qk, int qk_stride, const float* wq, const float* wk, float eps, const float* angles, int half, int layout,
+                         void* kpages, void* vpages, const int* kv_slot, int n_tokens, int nq, int nkv, int dk, int page_size,
+                         int keys_as_values, void* stream) {
+  if (n_tokens <= 0) return 0;
+  if (half < 0 || 2 * half > dk || (layout != ROTARY_INTERLEAVED && layout != ROTARY_HALVES) || (half > 0 && !angles) || dk > 2048)
+    return (int)cudaErrorInvalidValue;
+  const int warps = 4;
+  launch(qk_norm_store_kernel<T>, dim3(n_tokens), dim3(warps * 32), (size_t)warps * dk * sizeof(float), (cudaStream_t)stream, (T*)qk,
+         qk_stride, wq, wk, eps, angles, half, layout, (T*)kpages, (T*)vpages, kv_slot, nq, nkv, dk, page_size, keys_as_values);
+  return launch_status();
+}
+Q25_EXPORT int q25_biased_attention_qk_norm_store_f32(void* qk, int qs, const float* wq, const float* wk, float eps, const float* ang, int half, int layout,
+        void* kp, void* vp, const int* slot, int n, int nq, int nkv, int dk, int ps, int kav, void* s) {
+  return qk_norm_store<float>(qk, qs, wq, wk, eps, ang, half, layout, kp, vp, slot, n, nq, nkv, dk, ps, kav, s);
+}
+Q25_EXPORT int q25_biased_attention_qk_norm_store_bf16(void* qk, int qs, const float* wq, const float* wk, float eps, const float* ang, int half, int layout,
+        void* kp, void* vp, const int* slot, int n, int nq, int nkv, int dk, int ps, int kav, void* s) {
+  return qk_norm_store<bf16>(qk, qs, wq, wk, eps, ang, half, layout, kp, vp, slot, n, nq, nkv, dk, ps, kav, s);
 }
 
 // ================================================================================================
@@ -223,6 +293,7 @@ struct BiasedArgs {
   const int* items;  // runs: (entry, row tile) pairs; single tokens: entry indices
   int nq, nkv, page_size, window, keep_first;
   float scale_log2;
+  float cap_log2, scale_over_cap;   // scores squashed by cap * tanh(q.k * scale / cap): cap * log2(e) and scale / cap (cap_log2 0: not squashed)
   const float* r1;
   const float* r2;
   const float* sink;   // per query head, a score without key or value that joins the denominator (nullptr: none)
@@ -285,7 +356,7 @@ __device__ __forceinline__ void biased_load_tile(unsigned char* ks, unsigned cha
 template <int DK, int DV, int BN, bool FULL>
 __device__ __forceinline__ void biased_tile(const unsigned (&qf)[DK / 16][4], const unsigned char* ks, const unsigned char* vs,
                                             int key0, int rl, int rh, int p0, int p1, int window, int keep_first, float scale_log2,
-                                            float b10, float b20, float b11, float b21, float (&m)[2], float (&l)[2],
+                                            float cap_log2, float scale_over_cap, float b10, float b20, float b11, float b21, float (&m)[2], float (&l)[2],
                                             float (&o)[DV / 8][4]) {
   constexpr int PK = Tile<DK>::PITCH, PV = Tile<DV>::PITCH;
   const int lane = threadIdx.x & 31, t = lane & 3;
@@ -310,7 +381,8 @@ __device__ __forceinline__ void biased_tile(const unsigned (&qf)[DK / 16][4], co
     for (int e = 0; e < 4; ++e) {
       const float fd = (e < 2 ? d0 : d1) - (float)(j * 8 + (e & 1));
       const float b1 = e < 2 ? b10 : b11, b2 = e < 2 ? b20 : b21;
-      float v = fmaf(s[j][e], scale_log2, -b1 * __log2f(fmaf(b2, fd, 1.0f)));
+      float v = cap_log2 > 0.f ? cap_log2 * tanhf(s[j][e] * scale_over_cap) - b1 * __log2f(fmaf(b2, fd, 1.0f))
+                               : fmaf(s[j][e], scale_log2, -b1 * __log2f(fmaf(b2, fd, 1.0f)));
       if (!FULL) {
         const int kidx = key0 + j * 8 + 2 * t + (e & 1);
         const int dist = (e < 2 ? p0 : p1) - kidx;
@@ -429,9 +501,9 @@ __global__ void __launch_bounds__(128) biased_prefill_kernel(BiasedArgs a) {
     __syncthreads();
     walk.tile(i, BN, key0, rl, rh);
     if (tile_is_full(key0, BN, rl, rh, wp_min, wp_max, a.window, a.keep_first))
-      biased_tile<DK, DV, BN, true>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, b10, b20, b11, b21, m, l, o);
+      biased_tile<DK, DV, BN, true>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, a.cap_log2, a.scale_over_cap, b10, b20, b11, b21, m, l, o);
     else
-      biased_tile<DK, DV, BN, false>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, b10, b20, b11, b21, m, l, o);
+      biased_tile<DK, DV, BN, false>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, a.cap_log2, a.scale_over_cap, b10, b20, b11, b21, m, l, o);
     __syncthreads();
   }
   float l0 = quad_sum(l[0]), l1 = quad_sum(l[1]);
@@ -499,7 +571,7 @@ __global__ void __launch_bounds__(128) biased_decode_kernel(BiasedArgs a) {
     }
     __syncwarp();
     walk.tile(i, BN, key0, rl, rh);
-    biased_tile<DK, DV, BN, false>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, b10, b20, b11, b21, m, l, o);
+    biased_tile<DK, DV, BN, false>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, a.cap_log2, a.scale_over_cap, b10, b20, b11, b21, m, l, o);
     __syncwarp();
   }
   cp_async_wait<0>();
@@ -611,14 +683,16 @@ Q25_EXPORT int q25_biased_attention_mma_bf16(const void* qkv, int qkv_stride, vo
                                              int tw, const int* cu, const int* sp, const int* tiles, int n_tiles, const int* items,
                                              int n_items, int nq, int nkv, int dk, int dv, int ps, int window, int keep, float scale,
                                              const float* r1, const float* r2, const float* sink, int v_row, int n_splits, float* part_o,
-                                             float* part_ml, void* stream) {
+                                             float* part_ml, float softcap, void* stream) {
   if (n_tiles <= 0 && n_items <= 0) return 0;
   if (nkv <= 0 || nq % nkv || ps <= 0 || n_splits < 1 || (n_items > 0 && nq / nkv > 16) || v_row % 8) return (int)cudaErrorInvalidValue;
   BiasedArgs a;
   a.qkv = (const bf16*)qkv; a.qkv_stride = qkv_stride; a.out = (bf16*)out; a.kpages = (const bf16*)kp; a.vpages = (const bf16*)vp;
   a.block_table = bt; a.table_width = tw; a.cu_q = cu; a.q_start_pos = sp; a.items = nullptr;
   a.nq = nq; a.nkv = nkv; a.page_size = ps; a.window = window; a.keep_first = keep;
-  a.scale_log2 = scale * 1.4426950408889634f; a.r1 = r1; a.r2 = r2; a.sink = sink; a.v_row = v_row > 0 ? v_row : dv; a.n_splits = n_splits; a.part_o = part_o; a.part_ml = part_ml;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f; a.scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
+  a.r1 = r1; a.r2 = r2; a.sink = sink; a.v_row = v_row > 0 ? v_row : dv; a.n_splits = n_splits; a.part_o = part_o; a.part_ml = part_ml;
   cudaStream_t s = (cudaStream_t)stream;
 #define BIASED_CASE(K, V) if (dk == K && dv == V) return biased_mma_launch<K, V>(a, n_tiles, n_items, tiles, items, s);
   BIASED_SIZES(BIASED_CASE)

@@ -12,7 +12,7 @@
 
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                    float* __restrict__ x, int hidden, int vocab) {
+                                    float* __restrict__ x, int hidden, int vocab, float scale) {
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x;
@@ -20,7 +20,7 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // the host validates ids; never read outside
   const T* src = table + (size_t)id * hidden;
   float* dst = x + (size_t)row * hidden;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_f32(src[c]);
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_f32(src[c]) * scale;      // scale 1: the row as it is
 }
 
 // Four consecutive values as floats, and back (bf16: 8 bytes, float: 16 bytes at a time).
@@ -243,10 +243,11 @@ __global__ void add_norm_groups_kernel(float* __restrict__ x, const T* __restric
 }
 
 // Gated linear unit with clamped branches: gu is [n, 2*inter], gate in the first half of a row, up
-// in the second; g = min(g, limit), u = clamp(u, -limit, limit), out = g * sigmoid(alpha * g) * (u + 1).
+// in the second; g = min(g, limit), u = clamp(u, -limit, limit), out = g * sigmoid(alpha * g) * (u + shift)
+// (limit infinite, alpha 1 and shift 0: silu(g) * u).
 template <typename T, bool VEC>
 __global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out, int n, int inter, float limit, float alpha,
-                                   int paired) {
+                                   float shift, int paired) {
   pdl_trigger();
   pdl_wait();
   constexpr int STEP = VEC ? 4 : 1;                     // VEC: inter is a multiple of 4 and the rows start on 16-byte boundaries
@@ -268,7 +269,7 @@ __global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out
 #pragma unroll
     for (int k = 0; k < STEP; ++k) {
       const float gg = fminf(g[k], limit), uu = fminf(fmaxf(u[k], -limit), limit);
-      g[k] = gg / (1.0f + expf(-alpha * gg)) * (uu + 1.0f);
+      g[k] = gg / (1.0f + expf(-alpha * gg)) * (uu + shift);
     }
     if (VEC) store4<T>(out + i * 4, make_float4(g[0], g[1], g[2], g[3]));
     else out[i] = from_f32<T>(g[0]);
@@ -363,7 +364,7 @@ static int add_norm_groups(float* x, const void* delta, const float* dw, float d
 }
 
 template <typename T>
-static int glu_clamped(const void* gu, void* out, int n, int inter, float limit, float alpha, int paired, void* stream) {
+static int glu_clamped(const void* gu, void* out, int n, int inter, float limit, float alpha, float shift, int paired, void* stream) {
   if (n <= 0) return 0;
   if (paired && inter % 8) return (int)cudaErrorInvalidValue;
   const bool vec = inter % 4 == 0 && !(((uintptr_t)gu | (uintptr_t)out) & 15);
@@ -371,15 +372,15 @@ static int glu_clamped(const void* gu, void* out, int n, int inter, float limit,
   size_t blocks = (total + 255) / 256;
   const size_t most = (size_t)(device_sm_count() > 0 ? device_sm_count() : 148) * 16;
   if (blocks > most) blocks = most;
-  if (vec) launch(glu_clamped_kernel<T, true>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)gu, (T*)out, n, inter, limit, alpha, paired);
-  else launch(glu_clamped_kernel<T, false>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)gu, (T*)out, n, inter, limit, alpha, paired);
+  if (vec) launch(glu_clamped_kernel<T, true>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)gu, (T*)out, n, inter, limit, alpha, shift, paired);
+  else launch(glu_clamped_kernel<T, false>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)gu, (T*)out, n, inter, limit, alpha, shift, paired);
   return launch_status();
 }
 
 template <typename T>
-static int embed_gather(const void* table, const int* ids, float* x, int n, int hidden, int vocab, void* stream) {
+static int embed_gather(const void* table, const int* ids, float* x, int n, int hidden, int vocab, float scale, void* stream) {
   if (n <= 0) return 0;
-  launch(embed_gather_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, (const T*)table, ids, x, hidden, vocab);
+  launch(embed_gather_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, (const T*)table, ids, x, hidden, vocab, scale);
   return launch_status();
 }
 
@@ -412,8 +413,8 @@ static int silu_mul(const void* gu, void* out, int n, int inter, int paired, voi
   return launch_status();
 }
 
-Q25_EXPORT int q25_embed_gather_f32(const void* t, const int* ids, float* x, int n, int h, int v, void* s) { return embed_gather<float>(t, ids, x, n, h, v, s); }
-Q25_EXPORT int q25_embed_gather_bf16(const void* t, const int* ids, float* x, int n, int h, int v, void* s) { return embed_gather<bf16>(t, ids, x, n, h, v, s); }
+Q25_EXPORT int q25_embed_gather_f32(const void* t, const int* ids, float* x, int n, int h, int v, float sc, void* s) { return embed_gather<float>(t, ids, x, n, h, v, sc, s); }
+Q25_EXPORT int q25_embed_gather_bf16(const void* t, const int* ids, float* x, int n, int h, int v, float sc, void* s) { return embed_gather<bf16>(t, ids, x, n, h, v, sc, s); }
 Q25_EXPORT int q25_add_rmsnorm_f32(float* x, const void* d, const float* w, float eps, void* o, const int* rows, int n, int h, void* s) { return add_rmsnorm<float, true>(x, d, w, eps, o, rows, n, h, s); }
 Q25_EXPORT int q25_add_rmsnorm_bf16(float* x, const void* d, const float* w, float eps, void* o, const int* rows, int n, int h, void* s) { return add_rmsnorm<bf16, false>(x, d, w, eps, o, rows, n, h, s); }
 Q25_EXPORT int q25_silu_mul_f32(const void* gu, void* o, int n, int inter, int paired, void* s) { return silu_mul<float>(gu, o, n, inter, paired, s); }
@@ -423,8 +424,8 @@ Q25_EXPORT int q25_embed_position_norm_f32(const void* t, const void* pt, const 
 Q25_EXPORT int q25_embed_position_norm_bf16(const void* t, const void* pt, const int* ids, const int* pos, const float* w, float eps, float* x, int n, int h, int v, int mp, int g, void* s) { return embed_position_norm<bf16, false>(t, pt, ids, pos, w, eps, x, n, h, v, mp, g, s); }
 Q25_EXPORT int q25_add_norm_groups_f32(float* x, const void* d, const float* dw, float de, int dg, const float* w, float eps, int g, void* o, const int* rows, int n, int h, void* s) { return add_norm_groups<float, true>(x, d, dw, de, dg, w, eps, g, o, rows, n, h, s); }
 Q25_EXPORT int q25_add_norm_groups_bf16(float* x, const void* d, const float* dw, float de, int dg, const float* w, float eps, int g, void* o, const int* rows, int n, int h, void* s) { return add_norm_groups<bf16, false>(x, d, dw, de, dg, w, eps, g, o, rows, n, h, s); }
-Q25_EXPORT int q25_glu_clamped_f32(const void* gu, void* o, int n, int inter, float limit, float alpha, int paired, void* s) { return glu_clamped<float>(gu, o, n, inter, limit, alpha, paired, s); }
-Q25_EXPORT int q25_glu_clamped_bf16(const void* gu, void* o, int n, int inter, float limit, float alpha, int paired, void* s) { return glu_clamped<bf16>(gu, o, n, inter, limit, alpha, paired, s); }
+Q25_EXPORT int q25_glu_clamped_f32(const void* gu, void* o, int n, int inter, float limit, float alpha, float shift, int paired, void* s) { return glu_clamped<float>(gu, o, n, inter, limit, alpha, shift, paired, s); }
+Q25_EXPORT int q25_glu_clamped_bf16(const void* gu, void* o, int n, int inter, float limit, float alpha, float shift, int paired, void* s) { return glu_clamped<bf16>(gu, o, n, inter, limit, alpha, shift, paired, s); }
 
 // Streaming multiprocessors of the current device (0 if it cannot be read).
 Q25_EXPORT int q25_sm_count(void) { return device_sm_count(); }
@@ -447,5 +448,157 @@ Q25_EXPORT int q25_softcap(float* logits, long long total, float cap, void* s) {
   const size_t most = (size_t)(device_sm_count() > 0 ? device_sm_count() : 148) * 16;
   if (blocks > most) blocks = most;
   launch(softcap_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)s, logits, (size_t)total, cap);
+  return launch_status();
+}
+
+// ---- layer norm around the residual stream; several branches into one update; a stream that is mixed with another ----
+
+// (v - mean) / sqrt(var + eps) over the row_len floats of `row` (shared memory), var the mean of the squared
+// deviations: two passes, each a block sum in a fixed order.  Returns (mean, 1 / sqrt(var + eps)) to every thread.
+__device__ __forceinline__ float2 row_mean_inv(const float* row, int hidden, float eps, float* scratch) {
+  float s = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) s += row[c];
+  const float mean = block_sum(s, scratch) / (float)hidden;
+  float q = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) { const float d = row[c] - mean; q = fmaf(d, d, q); }
+  const float var = block_sum(q, scratch) / (float)hidden;
+  return make_float2(mean, 1.0f / sqrtf(var + eps));
+}
+
+// x += post(delta); out = ((x - mean) / sqrt(var + eps)) * w + b.  post(delta), when dw is given, is the layer norm of
+// the update with weight dw and bias db, times the vector ds when that is given (a learned scale per channel); without dw
+// the update is added as it is.  With `rows` only those rows are produced and x is left alone.  out == nullptr: only the addition.
+template <typename T>
+__global__ void add_layernorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ dw,
+                                     const float* __restrict__ db, const float* __restrict__ ds, float d_eps,
+                                     const float* __restrict__ w, const float* __restrict__ b, float eps,
+                                     T* __restrict__ out, const int* __restrict__ rows, int hidden) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ __align__(16) float ln_cache[];     // 2 * hidden floats + 32 scratch
+  float* row_cache = ln_cache;
+  float* d_cache = ln_cache + hidden;
+  float* scratch = d_cache + hidden;
+  const int r = blockIdx.x;
+  const int row = rows ? rows[r] : r;
+  float* xr = x + (size_t)row * hidden;
+  if (delta) {
+    const T* dr = delta + (size_t)row * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) d_cache[c] = to_f32(dr[c]);
+    float2 st = make_float2(0.f, 1.f);
+    if (dw) {
+      __syncthreads();
+      st = row_mean_inv(d_cache, hidden, d_eps, scratch);
+    }
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      float d = d_cache[c];
+      if (dw) {
+        d = (d - st.x) * st.y * dw[c] + db[c];
+        if (ds) d *= ds[c];
+      }
+      const float v = xr[c] + d;
+      row_cache[c] = v;
+      if (!rows) xr[c] = v;
+    }
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) row_cache[c] = xr[c];
+  }
+  if (!out) return;
+  __syncthreads();
+  const float2 st = row_mean_inv(row_cache, hidden, eps, scratch);
+  T* o = out + (size_t)r * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = from_f32<T>((row_cache[c] - st.x) * st.y * w[c] + b[c]);
+}
+
+template <typename T>
+static int add_layernorm(float* x, const void* delta, const float* dw, const float* db, const float* ds, float d_eps, const float* w,
+                         const float* b, float eps, void* out, const int* rows, int n_out, int hidden, void* stream) {
+  if (n_out <= 0) return 0;
+  if (out && (!w || !b)) return (int)cudaErrorInvalidValue;
+  if (dw && !db) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)(2 * hidden + 32) * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  if (smem > 48 * 1024) {
+    const cudaError_t e = cudaFuncSetAttribute(add_layernorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  launch(add_layernorm_kernel<T>, dim3(n_out), dim3(hidden >= 1024 ? 256 : 128), smem, (cudaStream_t)stream, x, (const T*)delta, dw, db,
+         ds, d_eps, w, b, eps, (T*)out, rows, hidden);
+  return launch_status();
+}
+Q25_EXPORT int q25_add_layernorm_f32(float* x, const void* d, const float* dw, const float* db, const float* ds, float de, const float* w, const float* b, float eps, void* o, const int* rows, int n, int h, void* s) { return add_layernorm<float>(x, d, dw, db, ds, de, w, b, eps, o, rows, n, h, s); }
+Q25_EXPORT int q25_add_layernorm_bf16(float* x, const void* d, const float* dw, const float* db, const float* ds, float de, const float* w, const float* b, float eps, void* o, const int* rows, int n, int h, void* s) { return add_layernorm<bf16>(x, d, dw, db, ds, de, w, b, eps, o, rows, n, h, s); }
+
+// out = (1 / n) * sum over the n branches of  branch_i / rms(branch_i) * w_i  (rms with eps inside the root), n <= 4:
+// the results of mixers that ran side by side on the same input become one update.
+struct BranchArgs {
+  const void* in[4];
+  const float* w[4];
+  int n;
+};
+template <typename T>
+__global__ void branch_mean_norm_kernel(BranchArgs a, T* __restrict__ out, int hidden, float eps) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * hidden;
+  float inv[4];
+  for (int i = 0; i < a.n; ++i) {
+    const T* p = (const T*)a.in[i] + base;
+    float q = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) { const float v = to_f32(p[c]); q = fmaf(v, v, q); }
+    inv[i] = 1.0f / sqrtf(block_sum(q, scratch) / (float)hidden + eps);
+  }
+  const float share = 1.0f / (float)a.n;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float acc = 0.f;
+    for (int i = 0; i < a.n; ++i) acc += to_f32(((const T*)a.in[i])[base + c]) * inv[i] * a.w[i][c];
+    out[base + c] = from_f32<T>(acc * share);
+  }
+}
+template <typename T>
+static int branch_mean_norm(const void* const* in, const float* const* w, int n, void* out, int rows, int hidden, float eps, void* stream) {
+  if (rows <= 0) return 0;
+  if (n < 1 || n > 4) return (int)cudaErrorInvalidValue;
+  BranchArgs a;
+  for (int i = 0; i < 4; ++i) { a.in[i] = i < n ? in[i] : nullptr; a.w[i] = i < n ? w[i] : nullptr; }
+  a.n = n;
+  launch(branch_mean_norm_kernel<T>, dim3(rows), dim3(hidden >= 1024 ? 256 : 128), 0, (cudaStream_t)stream, a, (T*)out, hidden, eps);
+  return launch_status();
+}
+Q25_EXPORT int q25_branch_mean_norm_f32(const void* const* in, const float* const* w, int n, void* o, int rows, int h, float eps, void* s) { return branch_mean_norm<float>(in, w, n, o, rows, h, eps, s); }
+Q25_EXPORT int q25_branch_mean_norm_bf16(const void* const* in, const float* const* w, int n, void* o, int rows, int h, float eps, void* s) { return branch_mean_norm<bf16>(in, w, n, o, rows, h, eps, s); }
+
+// cat[row] = [x[row] + post(delta)[row] | other[row]] in T, the input of a product that mixes the stream with another one
+// (x itself is updated too: the pending update is in afterwards); and x = y + bias after that product:
+template <typename T>
+__global__ void stream_pair_kernel(const float* __restrict__ x, const float* __restrict__ other, T* __restrict__ cat, int hidden) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    cat[row * 2 * hidden + c] = from_f32<T>(x[row * hidden + c]);
+    cat[row * 2 * hidden + hidden + c] = from_f32<T>(other[row * hidden + c]);
+  }
+}
+__global__ void stream_set_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ bias, int hidden) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) x[row * hidden + c] = y[row * hidden + c] + bias[c];
+}
+Q25_EXPORT int q25_stream_pair_f32(const float* x, const float* other, void* cat, int rows, int h, void* s) {
+  if (rows <= 0) return 0;
+  launch(stream_pair_kernel<float>, dim3(rows), dim3(128), 0, (cudaStream_t)s, x, other, (float*)cat, h);
+  return launch_status();
+}
+Q25_EXPORT int q25_stream_pair_bf16(const float* x, const float* other, void* cat, int rows, int h, void* s) {
+  if (rows <= 0) return 0;
+  launch(stream_pair_kernel<bf16>, dim3(rows), dim3(128), 0, (cudaStream_t)s, x, other, (bf16*)cat, h);
+  return launch_status();
+}
+Q25_EXPORT int q25_stream_set(float* x, const float* y, const float* bias, int rows, int h, void* s) {
+  if (rows <= 0) return 0;
+  launch(stream_set_kernel, dim3(rows), dim3(128), 0, (cudaStream_t)s, x, y, bias, h);
   return launch_status();
 }

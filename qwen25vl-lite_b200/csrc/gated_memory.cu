@@ -1,0 +1,347 @@
+// Matrix memories with gates that depend on the token: per head a state S [D, Dv] in float, carried from
+// token to token,
+//
+//     S_t = diag(a_t) S_(t-1) + b_t k_t v_t^T,          o_t = S_t^T q_t.
+//
+// Two kinds of gate:
+//   * per key channel (gated linear attention): a_t [D] comes as a table of decays in (0, 1), b_t = 1;
+//   * per head with a running maximum (the matrix memory of xLSTM): from the logarithms i_t, f_t of an input and
+//     a forget gate, m_t = max(f_t + m_(t-1), i_t) (m starts at 0), a_t = exp(f_t + m_(t-1) - m_t) for every
+//     channel, b_t = exp(i_t - m_t).  The normaliser n_t = a_t n_(t-1) + b_t k_t is one more column of S (its value
+//     is 1 for every token), so o_t's last entry is n_t . q_t.  The state keeps m too, as one more row of S.
+//
+// The walk (memory_scan_kernel): a CTA owns a request's run of tokens, one head and 32 columns of S; a thread
+// owns one column's entries in RPT rows, in registers.  The run is taken GM_TOKENS tokens at a time: the tokens' q,
+// k, decays and the 32 values are staged in shared memory as floats, every thread walks the tokens without a
+// barrier (S never leaves its registers), leaving its part of every o_t in shared memory; then the parts of the row
+// slices are added in slice order and o_t goes to memory as floats.  The order of every sum depends on the sizes
+// alone, so a token's result does not depend on where its run was cut or on the batch.
+//
+// The output (memory_output_kernel, a warp per token and head): o_t divided by max(|n_t . q_t|, exp(-m_t)) + 1e-6
+// where the memory has a normaliser; divided by its root mean square over the head's Dv channels (eps inside the
+// root); times a weight per channel; times silu or sigmoid of the token's gate channel; in T.
+//
+// Everything here is float but the projections the kernels read (q, k, v, the output gate) and the result.
+#include "common.cuh"
+#include "row_logits.cuh"
+
+#define GM_TOKENS 16
+#define GM_COLS 32
+
+__device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+// decay[n, c] = sigmoid(z)^(1 / tau), z = bias[c] + sum_r a2t[r, c] * low[n, r]: the low-rank projection's second
+// factor (transposed, float), the bias and the map into (0, 1) in one pass; computed as exp(log sigmoid(z) / tau).
+// A block takes 8 tokens, so that a column of a2t read from cache serves eight of them.
+template <typename T>
+__global__ void gla_decay_kernel(const T* __restrict__ x, int x_stride, int low_off, int rank, const float* __restrict__ a2t,
+                                 const float* __restrict__ bias, float inv_tau, float* __restrict__ decay, int n_tokens, int channels) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ __align__(16) float low_s[];     // [8][rank]
+  const int n0 = blockIdx.x * 8;
+  for (int i = threadIdx.x; i < 8 * rank; i += blockDim.x) {
+    const int t = i / rank, r = i % rank;
+    low_s[i] = n0 + t < n_tokens ? to_f32(x[(size_t)(n0 + t) * x_stride + low_off + r]) : 0.f;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    float z[8];
+    const float b = bias ? bias[c] : 0.f;
+#pragma unroll
+    for (int t = 0; t < 8; ++t) z[t] = b;
+    for (int r = 0; r < rank; ++r) {
+      const float w = a2t[(size_t)r * channels + c];
+#pragma unroll
+      for (int t = 0; t < 8; ++t) z[t] = fmaf(w, low_s[t * rank + r], z[t]);
+    }
+#pragma unroll
+    for (int t = 0; t < 8; ++t)
+      if (n0 + t < n_tokens) decay[(size_t)(n0 + t) * channels + c] = expf(log_sigmoid(z[t]) * inv_tau);
+  }
+}
+
+// out[n, j] = bias[j] + w[j, :] . h[n, :] for a few float rows w (gates of a recurrence), float results.
+template <typename T, int TOK>
+__global__ void __launch_bounds__(256)
+row_dots_kernel(const T* __restrict__ h, const float* __restrict__ w, const float* __restrict__ bias, float* __restrict__ out,
+                int n_tokens, int hidden, int rows) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ __align__(16) float dots_smem[];
+  route_logits<T, TOK>(h, w, nullptr, dots_smem, n_tokens, hidden, rows);
+  const float* zs = dots_smem + TOK * ((hidden + 3) & ~3);
+  const int n0 = blockIdx.x * TOK;
+  for (int i = threadIdx.x; i < TOK * rows; i += 256) {
+    const int t = i / rows, j = i % rows;
+    if (n0 + t < n_tokens) out[(size_t)(n0 + t) * rows + j] = zs[t * (ROW_LOGITS_MAX + 1) + j] + (bias ? bias[j] : 0.f);
+  }
+}
+
+struct MemoryArgs {
+  const void* x;            // [N, x_stride] in T: q, k, v at their offsets, heads side by side
+  int x_stride, q_off, k_off, v_off;
+  const float* decay;       // per key channel [N, H * D] (gates per channel), or nullptr
+  const float* gates;       // per head [N, 2 * H]: what becomes log i, then what becomes log f (gates per head), or nullptr
+  float cap;                // the per-head gates are squashed by cap * tanh(. / cap) first (0: taken as they are)
+  float q_scale;
+  float* state;             // [slots][H][D + extra][Dv + extra]
+  const int* cu_q;
+  const int* slot_ids;
+  float* o_raw;             // [N, H, Dv + extra]
+  float* m_exp;             // [N, H]: exp(-m_t) (gates per head)
+  int H, D, Dv, extra;
+};
+
+// (a, b) stands for x -> max(x + a, b); `first` then `second` is x -> max(x + a1 + a2, max(b1 + a2, b2)).
+__device__ __forceinline__ void maxplus_after(float& a, float& b, float a1, float b1) {
+  b = fmaxf(b1 + a, b);
+  a = a1 + a;
+}
+
+template <typename T, int RPT, bool PER_HEAD>
+__global__ void memory_scan_kernel(MemoryArgs p) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ __align__(16) float gm_smem[];
+  const int DG = blockDim.y, Dp = DG * RPT;
+  const int head = blockIdx.x, seq = blockIdx.y;
+  const int lane = threadIdx.x, g = threadIdx.y, tid = g * GM_COLS + lane, n_threads = GM_COLS * DG;
+  const int cols = p.Dv + p.extra, col0 = blockIdx.z * GM_COLS, col = col0 + lane;
+  const bool col_ok = col < cols;
+  float* q_s = gm_smem;                                  // [GM_TOKENS][Dp]
+  float* k_s = q_s + GM_TOKENS * Dp;
+  float* a_s = k_s + GM_TOKENS * Dp;                     // per channel: [GM_TOKENS][Dp]; per head: [GM_TOKENS] a_t, [GM_TOKENS] b_t, m
+  float* v_s = a_s + (PER_HEAD ? 2 * GM_TOKENS + 4 : GM_TOKENS * Dp);      // [GM_TOKENS][GM_COLS]
+  float* part = v_s + GM_TOKENS * GM_COLS;               // [GM_TOKENS][DG][GM_COLS]
+  const int begin = p.cu_q[seq], end = p.cu_q[seq + 1];
+  float* st = p.state + ((size_t)p.slot_ids[seq] * p.H + head) * (size_t)(p.D + p.extra) * cols;
+  const T* x = (const T*)p.x;
+
+  float S[RPT];
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const int r = g * RPT + i;
+    S[i] = (r < p.D && col_ok) ? st[(size_t)r * cols + col] : 0.f;
+  }
+  float m_carry = PER_HEAD ? st[(size_t)p.D * cols + col0] : 0.f;     // every column keeps a copy of m; the CTA reads its first
+
+  for (int t0 = begin; t0 < end; t0 += GM_TOKENS) {
+    const int nt = min(GM_TOKENS, end - t0);
+    __syncthreads();                                     // the chunk before has been read out
+    for (int i = tid; i < nt * Dp; i += n_threads) {
+      const int t = i / Dp, r = i % Dp;
+      const size_t row = (size_t)(t0 + t) * p.x_stride;
+      const bool ok = r < p.D;
+      q_s[i] = ok ? to_f32(x[row + p.q_off + head * p.D + r]) * p.q_scale : 0.f;
+      k_s[i] = ok ? to_f32(x[row + p.k_off + head * p.D + r]) : 0.f;
+      if (!PER_HEAD) a_s[i] = ok ? p.decay[((size_t)(t0 + t) * p.H + head) * p.D + r] : 0.f;
+    }
+    for (int i = tid; i < nt * GM_COLS; i += n_threads) {
+      const int t = i / GM_COLS, c = col0 + i % GM_COLS;
+      v_s[i] = c < p.Dv ? to_f32(x[(size_t)(t0 + t) * p.x_stride + p.v_off + head * p.Dv + c]) : (c < cols ? 1.f : 0.f);
+    }
+    if (PER_HEAD && g == 0) {
+      // the chunk's gates by the first warp: lane t holds token t's map x -> max(x + f_t, i_t); an inclusive scan composes
+      // them, applied to the m that came in it gives every m_t at once
+      float li = -INFINITY, lf = 0.f;
+      if (lane < nt) {
+        const float* gt = p.gates + (size_t)(t0 + lane) * 2 * p.H;
+        float zi = gt[head], zf = gt[p.H + head];
+        if (p.cap > 0.f) { zi = p.cap * tanhf(zi / p.cap); zf = p.cap * tanhf(zf / p.cap); }
+        li = zi;
+        lf = log_sigmoid(zf);
+      }
+      float a = lf, b = li;
+#pragma unroll
+      for (int o = 1; o < GM_TOKENS; o <<= 1) {
+        const float a1 = __shfl_up_sync(0xffffffffu, a, o), b1 = __shfl_up_sync(0xffffffffu, b, o);
+        if (lane >= o) maxplus_after(a, b, a1, b1);
+      }
+      const float m_t = fmaxf(m_carry + a, b);
+      float m_prev = __shfl_up_sync(0xffffffffu, m_t, 1);
+      if (lane == 0) m_prev = m_carry;
+      if (lane < nt) {
+        a_s[lane] = expf(lf + m_prev - m_t);
+        a_s[GM_TOKENS + lane] = expf(li - m_t);
+        if (blockIdx.z == 0) p.m_exp[(size_t)(t0 + lane) * p.H + head] = expf(-m_t);
+      }
+      if (lane == nt - 1) a_s[2 * GM_TOKENS] = m_t;
+    }
+    __syncthreads();
+    if (PER_HEAD) m_carry = a_s[2 * GM_TOKENS];
+    for (int t = 0; t < nt; ++t) {
+      const float4* q4 = reinterpret_cast<const float4*>(q_s + t * Dp + g * RPT);
+      const float4* k4 = reinterpret_cast<const float4*>(k_s + t * Dp + g * RPT);
+      const float4* a4 = reinterpret_cast<const float4*>(a_s + t * Dp + g * RPT);
+      const float v = PER_HEAD ? v_s[t * GM_COLS + lane] * a_s[GM_TOKENS + t] : v_s[t * GM_COLS + lane];
+      const float a_head = PER_HEAD ? a_s[t] : 0.f;
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < RPT / 4; ++i) {
+        const float4 qq = q4[i], kk = k4[i];
+        float4 aa;
+        if (PER_HEAD) aa = make_float4(a_head, a_head, a_head, a_head);
+        else aa = a4[i];
+        S[4 * i + 0] = fmaf(aa.x, S[4 * i + 0], kk.x * v); acc = fmaf(S[4 * i + 0], qq.x, acc);
+        S[4 * i + 1] = fmaf(aa.y, S[4 * i + 1], kk.y * v); acc = fmaf(S[4 * i + 1], qq.y, acc);
+        S[4 * i + 2] = fmaf(aa.z, S[4 * i + 2], kk.z * v); acc = fmaf(S[4 * i + 2], qq.z, acc);
+        S[4 * i + 3] = fmaf(aa.w, S[4 * i + 3], kk.w * v); acc = fmaf(S[4 * i + 3], qq.w, acc);
+      }
+      part[(t * DG + g) * GM_COLS + lane] = acc;
+    }
+    __syncthreads();
+    if (col_ok) {
+      for (int t = g; t < nt; t += DG) {
+        float o = 0.f;
+        for (int s = 0; s < DG; ++s) o += part[(t * DG + s) * GM_COLS + lane];
+        p.o_raw[((size_t)(t0 + t) * p.H + head) * cols + col] = o;
+      }
+    }
+  }
+  if (col_ok) {
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      const int r = g * RPT + i;
+      if (r < p.D) st[(size_t)r * cols + col] = S[i];
+    }
+    if (PER_HEAD && g == 0) st[(size_t)p.D * cols + col] = m_carry;
+  }
+}
+
+// A warp per (token, head).  act: 0 = silu of the gate channel, 1 = sigmoid.
+template <typename T>
+__global__ void memory_output_kernel(const float* __restrict__ o_raw, const float* __restrict__ m_exp, const T* __restrict__ x,
+                                     int x_stride, int g_off, const float* __restrict__ weight, T* __restrict__ out, int n_tokens,
+                                     int H, int Dv, int extra, float eps, int act) {
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (item >= (long long)n_tokens * H) return;
+  const int n = (int)(item / H), head = (int)(item % H);
+  const float* o = o_raw + (size_t)item * (Dv + extra);
+  float inv_den = 1.f;
+  if (extra) inv_den = 1.0f / (fmaxf(fabsf(o[Dv]), m_exp[item]) + 1e-6f);
+  float sq = 0.f;
+  for (int c = lane; c < Dv; c += 32) { const float v = o[c] * inv_den; sq = fmaf(v, v, sq); }
+  sq = warp_sum(sq);
+  const float inv = inv_den / sqrtf(sq / (float)Dv + eps);
+  const T* gate = x + (size_t)n * x_stride + g_off + head * Dv;
+  T* dst = out + ((size_t)n * H + head) * Dv;
+  for (int c = lane; c < Dv; c += 32) {
+    const float z = to_f32(gate[c]);
+    const float s = 1.0f / (1.0f + expf(-z));
+    dst[c] = from_f32<T>(o[c] * inv * weight[head * Dv + c] * (act == 0 ? z * s : s));
+  }
+}
+
+template <typename T>
+static int gla_decay(const void* x, int x_stride, int low_off, int rank, const float* a2t, const float* bias, float tau, float* decay,
+                     int n_tokens, int channels, void* stream) {
+  if (n_tokens <= 0) return 0;
+  if (rank <= 0 || rank > 1024 || !(tau > 0.f)) return (int)cudaErrorInvalidValue;
+  launch(gla_decay_kernel<T>, dim3((n_tokens + 7) / 8), dim3(channels >= 256 ? 256 : 128), (size_t)8 * rank * sizeof(float), (cudaStream_t)stream,
+         (const T*)x, x_stride, low_off, rank, a2t, bias, 1.0f / tau, decay, n_tokens, channels);
+  return launch_status();
+}
+Q25_EXPORT int q25_memory_gla_decay_f32(const void* x, int xs, int off, int rank, const float* a2t, const float* b, float tau, float* d, int n, int ch, void* s) {
+  return gla_decay<float>(x, xs, off, rank, a2t, b, tau, d, n, ch, s);
+}
+Q25_EXPORT int q25_memory_gla_decay_bf16(const void* x, int xs, int off, int rank, const float* a2t, const float* b, float tau, float* d, int n, int ch, void* s) {
+  return gla_decay<bf16>(x, xs, off, rank, a2t, b, tau, d, n, ch, s);
+}
+
+template <typename T, int TOK>
+static int row_dots_shape(const void* h, const float* w, const float* bias, float* out, int n_tokens, int hidden, int rows, cudaStream_t s) {
+  const size_t smem = (size_t)TOK * (((hidden + 3) & ~3) + ROW_LOGITS_MAX + 1) * sizeof(float);
+  if (smem > 200 * 1024) return -1;
+  if (smem > 48 * 1024) {
+    const cudaError_t e = cudaFuncSetAttribute(row_dots_kernel<T, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  launch(row_dots_kernel<T, TOK>, dim3((n_tokens + TOK - 1) / TOK), dim3(256), smem, s, (const T*)h, w, bias, out, n_tokens, hidden, rows);
+  return launch_status();
+}
+template <typename T>
+static int row_dots(const void* h, const float* w, const float* bias, float* out, int n_tokens, int hidden, int rows, void* stream) {
+  if (n_tokens <= 0) return 0;
+  if (rows <= 0 || rows > ROW_LOGITS_MAX) return (int)cudaErrorInvalidValue;
+  int rc = -1;
+  if (n_tokens >= 512) rc = row_dots_shape<T, 4>(h, w, bias, out, n_tokens, hidden, rows, (cudaStream_t)stream);
+  if (rc == -1) rc = row_dots_shape<T, 1>(h, w, bias, out, n_tokens, hidden, rows, (cudaStream_t)stream);
+  return rc == -1 ? (int)cudaErrorInvalidValue : rc;
+}
+Q25_EXPORT int q25_memory_row_dots_f32(const void* h, const float* w, const float* b, float* out, int n, int hidden, int rows, void* s) {
+  return row_dots<float>(h, w, b, out, n, hidden, rows, s);
+}
+Q25_EXPORT int q25_memory_row_dots_bf16(const void* h, const float* w, const float* b, float* out, int n, int hidden, int rows, void* s) {
+  return row_dots<bf16>(h, w, b, out, n, hidden, rows, s);
+}
+
+template <typename T, int RPT, bool PER_HEAD>
+static int memory_scan_shape(const MemoryArgs& p, int n_seqs, cudaStream_t s) {
+  const int DG = (p.D + RPT - 1) / RPT, Dp = DG * RPT;
+  const int cols = p.Dv + p.extra;
+  const size_t floats = (size_t)2 * GM_TOKENS * Dp + (PER_HEAD ? 2 * GM_TOKENS + 4 : GM_TOKENS * Dp) + GM_TOKENS * GM_COLS +
+                        (size_t)GM_TOKENS * DG * GM_COLS;
+  const size_t smem = floats * sizeof(float);
+  if (smem > 200 * 1024 || DG > 16) return (int)cudaErrorInvalidValue;
+  if (smem > 48 * 1024) {
+    const cudaError_t e = cudaFuncSetAttribute(memory_scan_kernel<T, RPT, PER_HEAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  launch(memory_scan_kernel<T, RPT, PER_HEAD>, dim3(p.H, n_seqs, (cols + GM_COLS - 1) / GM_COLS), dim3(GM_COLS, DG), smem, s, p);
+  return launch_status();
+}
+
+// per_head 0: decays per key channel from `decay`; 1: gates per head from `gates`, with a normaliser column and m in the state.
+template <typename T>
+static int memory_scan(const void* x, int x_stride, int q_off, int k_off, int v_off, const float* decay, const float* gates, float cap,
+                       float q_scale, float* state, const int* cu_q, const int* slot_ids, float* o_raw, float* m_exp, int n_seqs, int H,
+                       int D, int Dv, int per_head, void* stream) {
+  if (n_seqs <= 0) return 0;
+  if (H <= 0 || D <= 0 || Dv <= 0 || D > 512 || (per_head ? (!gates || !m_exp) : !decay)) return (int)cudaErrorInvalidValue;
+  MemoryArgs p;
+  p.x = x; p.x_stride = x_stride; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off; p.decay = decay; p.gates = gates; p.cap = cap;
+  p.q_scale = q_scale; p.state = state; p.cu_q = cu_q; p.slot_ids = slot_ids; p.o_raw = o_raw; p.m_exp = m_exp;
+  p.H = H; p.D = D; p.Dv = Dv; p.extra = per_head ? 1 : 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (per_head) {
+    if (D <= 64) return memory_scan_shape<T, 16, true>(p, n_seqs, s);
+    if (D <= 128) return memory_scan_shape<T, 32, true>(p, n_seqs, s);
+    return memory_scan_shape<T, 64, true>(p, n_seqs, s);
+  }
+  if (D <= 64) return memory_scan_shape<T, 16, false>(p, n_seqs, s);
+  if (D <= 128) return memory_scan_shape<T, 32, false>(p, n_seqs, s);
+  return memory_scan_shape<T, 64, false>(p, n_seqs, s);
+}
+Q25_EXPORT int q25_memory_scan_f32(const void* x, int xs, int qo, int ko, int vo, const float* decay, const float* gates, float cap, float qsc,
+                                   float* state, const int* cu, const int* slots, float* o_raw, float* m_exp, int n_seqs, int H, int D, int Dv,
+                                   int per_head, void* s) {
+  return memory_scan<float>(x, xs, qo, ko, vo, decay, gates, cap, qsc, state, cu, slots, o_raw, m_exp, n_seqs, H, D, Dv, per_head, s);
+}
+Q25_EXPORT int q25_memory_scan_bf16(const void* x, int xs, int qo, int ko, int vo, const float* decay, const float* gates, float cap, float qsc,
+                                    float* state, const int* cu, const int* slots, float* o_raw, float* m_exp, int n_seqs, int H, int D, int Dv,
+                                    int per_head, void* s) {
+  return memory_scan<bf16>(x, xs, qo, ko, vo, decay, gates, cap, qsc, state, cu, slots, o_raw, m_exp, n_seqs, H, D, Dv, per_head, s);
+}
+
+template <typename T>
+static int memory_output(const float* o_raw, const float* m_exp, const void* x, int x_stride, int g_off, const float* weight, void* out,
+                         int n_tokens, int H, int Dv, int extra, float eps, int act, void* stream) {
+  if (n_tokens <= 0) return 0;
+  if (extra && !m_exp) return (int)cudaErrorInvalidValue;
+  const long long items = (long long)n_tokens * H;
+  launch(memory_output_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, (cudaStream_t)stream, o_raw, m_exp, (const T*)x, x_stride,
+         g_off, weight, (T*)out, n_tokens, H, Dv, extra, eps, act);
+  return launch_status();
+}
+Q25_EXPORT int q25_memory_output_f32(const float* o, const float* me, const void* x, int xs, int go, const float* w, void* out, int n, int H, int Dv,
+                                     int extra, float eps, int act, void* s) {
+  return memory_output<float>(o, me, x, xs, go, w, out, n, H, Dv, extra, eps, act, s);
+}
+Q25_EXPORT int q25_memory_output_bf16(const float* o, const float* me, const void* x, int xs, int go, const float* w, void* out, int n, int H, int Dv,
+                                      int extra, float eps, int act, void* s) {
+  return memory_output<bf16>(o, me, x, xs, go, w, out, n, H, Dv, extra, eps, act, s);
+}

@@ -18,8 +18,9 @@
 // row falls into, so a token's result does not depend on the batch.  The bfloat16 products run on
 // the tensor cores (mma.sync m16n8k16, float accumulators) with the same layout.
 #include "attention_decode.cuh"
+#include "row_logits.cuh"
 
-#define MOE_MAX_EXPERTS 256
+#define MOE_MAX_EXPERTS ROW_LOGITS_MAX
 #define MOE_MAX_TOP 16
 
 // One block of 8 warps per TOK tokens (4 in steps of many tokens, where a row of the router read from
@@ -36,50 +37,11 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, cons
   pdl_trigger();
   pdl_wait();
   extern __shared__ __align__(16) float route_smem[];       // TOK rows of hidden floats, then TOK x (MOE_MAX_EXPERTS + 1) logits
+  route_logits<T, TOK>(h, router, shared_gate, route_smem, n_tokens, hidden, experts);
   const int pitch = (hidden + 3) & ~3;
-  float* xs = route_smem;
   float* zs = route_smem + TOK * pitch;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * TOK;
-  for (int i = 0; i < TOK; ++i) {
-    const int n = min(n0 + i, n_tokens - 1);
-    const T* row = h + (size_t)n * hidden;
-    for (int c = threadIdx.x; c < hidden; c += 256) xs[i * pitch + c] = to_f32(row[c]);
-  }
-  __syncthreads();
-  const int n_dots = experts + (shared_gate ? 1 : 0);
-  const bool vec = hidden % 4 == 0 && !(((uintptr_t)router | (uintptr_t)shared_gate) & 15);
-  for (int e = warp; e < n_dots; e += 8) {
-    const float* w = e < experts ? router + (size_t)e * hidden : shared_gate;
-    float acc[TOK];
-#pragma unroll
-    for (int i = 0; i < TOK; ++i) acc[i] = 0.f;
-    if (vec) {
-#pragma unroll 8
-      for (int c = lane * 4; c < hidden; c += 128) {
-        const float4 wv = *reinterpret_cast<const float4*>(w + c);
-#pragma unroll
-        for (int i = 0; i < TOK; ++i) {
-          const float4 xv = *reinterpret_cast<const float4*>(xs + i * pitch + c);
-          acc[i] = fmaf(wv.x, xv.x, acc[i]);
-          acc[i] = fmaf(wv.y, xv.y, acc[i]);
-          acc[i] = fmaf(wv.z, xv.z, acc[i]);
-          acc[i] = fmaf(wv.w, xv.w, acc[i]);
-        }
-      }
-    } else {
-      for (int c = lane; c < hidden; c += 32) {
-#pragma unroll
-        for (int i = 0; i < TOK; ++i) acc[i] = fmaf(w[c], xs[i * pitch + c], acc[i]);
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < TOK; ++i) {
-      const float z = warp_sum(acc[i]);
-      if (lane == 0) zs[i * (MOE_MAX_EXPERTS + 1) + e] = z;
-    }
-  }
-  __syncthreads();
   if (warp >= TOK || n0 + warp >= n_tokens) return;
   const int n = n0 + warp;
   float* z_row = zs + warp * (MOE_MAX_EXPERTS + 1);
@@ -102,6 +64,114 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, cons
       topk_w[(size_t)n * top + k] = 1.0f / (1.0f + expf(-best));
       z_row[arg] = -INFINITY;
       atomicAdd(&counts[arg], 1);
+    }
+    __syncwarp();
+  }
+}
+
+// The router of a mixture whose scores are a softmax over all `outputs` router rows, the last `outputs - experts` of
+// which stand for experts without matrices (a choice among them takes no row of the grouped products).  The choice looks
+// at score + correction[e]; the rows form `groups` equal runs of neighbours, a run's mark is its largest such number, and
+// only the `keep` runs with the largest marks can be chosen from (the others count as minus infinity).  The `top`
+// largest are chosen (ties to the lower index, among runs too); a choice weighs in with its plain score.  counts: one per
+// expert with matrices.  One block of 8 warps per TOK tokens as above, then a warp per token.
+template <typename T, int TOK>
+__global__ void __launch_bounds__(256)
+moe_route_softmax_kernel(const T* __restrict__ h, const float* __restrict__ router, const float* __restrict__ correction,
+                         int* __restrict__ topk_idx, float* __restrict__ topk_w, int* __restrict__ counts, int n_tokens, int hidden,
+                         int experts, int outputs, int top, int groups, int keep) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ __align__(16) float route_smem[];       // TOK rows of hidden floats, then TOK x 3 x (MOE_MAX_EXPERTS + 1) numbers
+  route_logits<T, TOK>(h, router, nullptr, route_smem, n_tokens, hidden, outputs);
+  const int pitch = (hidden + 3) & ~3;
+  float* zs = route_smem + TOK * pitch;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * TOK;
+  if (warp >= TOK || n0 + warp >= n_tokens) return;
+  const int n = n0 + warp;
+  float* score = zs + warp * (MOE_MAX_EXPERTS + 1);                          // logits, then scores
+  float* choice = zs + (TOK + 2 * warp) * (MOE_MAX_EXPERTS + 1);             // score + correction
+  float* mark = choice + (MOE_MAX_EXPERTS + 1);                              // a run's mark
+  float top_z = -INFINITY;
+  for (int e = lane; e < outputs; e += 32) top_z = fmaxf(top_z, score[e]);
+  top_z = warp_max(top_z);
+  float sum = 0.f;
+  for (int e = lane; e < outputs; e += 32) { const float p = expf(score[e] - top_z); score[e] = p; sum += p; }
+  sum = warp_sum(sum);
+  __syncwarp();
+  for (int e = lane; e < outputs; e += 32) {
+    const float s = score[e] / sum;
+    score[e] = s;
+    choice[e] = s + (correction ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  if (groups > 1) {
+    const int per = outputs / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float best = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, choice[e]);
+      mark[g] = best;
+    }
+    __syncwarp();
+    // the kept runs one after the other; every lane holds the same set: bit g % 32 of word g / 32
+    unsigned kept[MOE_MAX_EXPERTS / 32];
+#pragma unroll
+    for (int i = 0; i < MOE_MAX_EXPERTS / 32; ++i) kept[i] = 0u;
+    for (int k = 0; k < keep; ++k) {
+      float best = -INFINITY;
+      int arg = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32) {
+        bool taken = false;
+#pragma unroll
+        for (int i = 0; i < MOE_MAX_EXPERTS / 32; ++i) if (i == (g >> 5)) taken = (kept[i] >> (g & 31)) & 1u;
+        const float v = mark[g];
+        if (!taken && v > best) { best = v; arg = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+      }
+      if (arg != 0x7fffffff) {
+#pragma unroll
+        for (int i = 0; i < MOE_MAX_EXPERTS / 32; ++i) if (i == (arg >> 5)) kept[i] |= 1u << (arg & 31);
+      }
+    }
+    for (int e = lane; e < outputs; e += 32) {
+      const int g = e / per;
+      bool ok = false;
+#pragma unroll
+      for (int i = 0; i < MOE_MAX_EXPERTS / 32; ++i) if (i == (g >> 5)) ok = (kept[i] >> (g & 31)) & 1u;
+      if (!ok) choice[e] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int e = lane; e < outputs; e += 32) {
+      const float c = choice[e];
+      if (c > best) { best = c; arg = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    if (lane == 0) {
+      // fewer choosable rows than `top` (the host refuses such sizes): the choice is row 0 with weight 0
+      const bool none = arg == 0x7fffffff;
+      topk_idx[(size_t)n * top + k] = none ? 0 : arg;
+      topk_w[(size_t)n * top + k] = none ? 0.f : score[arg];
+      if (!none) {
+        choice[arg] = -INFINITY;
+        if (arg < experts) atomicAdd(&counts[arg], 1);
+      } else {
+        atomicAdd(&counts[0], 1);
+      }
     }
     __syncwarp();
   }
@@ -131,12 +201,13 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts, int* __restrict_
 }
 
 __global__ void moe_scatter_kernel(const int* __restrict__ topk_idx, const int* __restrict__ plan, int* __restrict__ cursor,
-                                   int* __restrict__ row_pair, int* __restrict__ pair_row, int n_pairs) {
+                                   int* __restrict__ row_pair, int* __restrict__ pair_row, int n_pairs, int experts) {
   pdl_trigger();
   pdl_wait();
   const int pair = blockIdx.x * blockDim.x + threadIdx.x;
   if (pair >= n_pairs) return;
   const int e = topk_idx[pair];
+  if (e >= experts) { pair_row[pair] = -1; return; }      // a choice beyond the experts that have matrices takes no row
   const int r = plan[1 + e] + atomicAdd(&cursor[e], 1);
   row_pair[r] = pair;
   pair_row[pair] = r;
@@ -149,7 +220,7 @@ template <typename T, bool GATE_UP, int BM, int BN, int BK, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 moe_grouped_fma_kernel(const T* __restrict__ A, const T* __restrict__ W0, const T* __restrict__ W1, void* __restrict__ out_,
                        const int* __restrict__ plan, const int* __restrict__ row_pair, const float* __restrict__ topk_w,
-                       int experts, int top, int N, int K, long long w_stride, float limit, float alpha) {
+                       int experts, int top, int N, int K, long long w_stride, float limit, float alpha, float shift) {
   pdl_trigger();
   pdl_wait();
   constexpr int THREADS = (BM / TM) * (BN / TN);
@@ -166,7 +237,7 @@ moe_grouped_fma_kernel(const T* __restrict__ A, const T* __restrict__ W0, const 
     const int pair = row_pair[m0 + r];
     if (GATE_UP) {
       src_row[r] = pair < 0 ? -1 : pair / top;
-      src_w[r] = pair < 0 ? 0.f : topk_w[pair];
+      src_w[r] = pair < 0 ? 0.f : (topk_w ? topk_w[pair] : 1.f);      // no weights: the rows as they are
     } else {
       src_row[r] = pair < 0 ? -1 : m0 + r;
       src_w[r] = 1.f;
@@ -228,7 +299,7 @@ moe_grouped_fma_kernel(const T* __restrict__ A, const T* __restrict__ W0, const 
       if (GATE_UP) {
         const float g = fminf(acc0[i][j], limit);
         const float u = fminf(fmaxf(acc1[i][j], -limit), limit);
-        reinterpret_cast<T*>(out_)[(size_t)(m0 + r) * N + gn] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+        reinterpret_cast<T*>(out_)[(size_t)(m0 + r) * N + gn] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + shift));
       } else {
         reinterpret_cast<float*>(out_)[(size_t)(m0 + r) * N + gn] = acc0[i][j];
       }
@@ -245,7 +316,7 @@ __global__ void moe_gather_kernel(const bf16* __restrict__ h, const int* __restr
   pdl_wait();
   const int pair = row_pair[blockIdx.x];
   if (pair < 0) return;
-  const float w = topk_w[pair];
+  const float w = topk_w ? topk_w[pair] : 1.f;
   const bf16* src = h + (size_t)(pair / top) * K;
   bf16* dst = sorted + (size_t)blockIdx.x * K;
   for (int c = threadIdx.x * 8; c < K; c += blockDim.x * 8) {
@@ -273,7 +344,7 @@ template <bool GATE_UP, int BM, int WARPS_M, int STAGES>
 __global__ void __launch_bounds__(128)
 moe_grouped_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W0, const bf16* __restrict__ W1, void* __restrict__ out_,
                        const int* __restrict__ plan, const int* __restrict__ row_pair, int experts, int N, int K, long long w_stride,
-                       float limit, float alpha) {
+                       float limit, float alpha, float shift) {
   pdl_trigger();
   pdl_wait();
   constexpr int BN = 64, BK = 64, P = BK * 2 + 16;            // pitch in bytes: an odd number of 16-byte chunks
@@ -380,7 +451,7 @@ moe_grouped_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W0, 
         if (GATE_UP) {
           const float g0 = fminf(v0, limit), g1 = fminf(v1, limit);
           const float u0 = fminf(fmaxf(acc1[i][j][2 * half], -limit), limit), u1 = fminf(fmaxf(acc1[i][j][2 * half + 1], -limit), limit);
-          const float y0 = g0 / (1.0f + expf(-alpha * g0)) * (u0 + 1.0f), y1 = g1 / (1.0f + expf(-alpha * g1)) * (u1 + 1.0f);
+          const float y0 = g0 / (1.0f + expf(-alpha * g0)) * (u0 + shift), y1 = g1 / (1.0f + expf(-alpha * g1)) * (u1 + shift);
           bf16* o = reinterpret_cast<bf16*>(out_) + (size_t)(m0 + r) * N + gn;
           if (gn + 1 < N && N % 2 == 0) *reinterpret_cast<unsigned*>(o) = pack_bf16(y0, y1);
           else { o[0] = __float2bfloat16_rn(y0); if (gn + 1 < N) o[1] = __float2bfloat16_rn(y1); }
@@ -433,6 +504,31 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
   }
 }
 
+// out[n, :] = sum over the token's choices, in their order, of w[pair] * (y[row of the pair, :], or the token's own
+// input h[n, :] when the pair has no row: a choice that stands for an expert without matrices), in T.
+template <typename T>
+__global__ void moe_combine_weighted_kernel(const float* __restrict__ y, const int* __restrict__ pair_row, const float* __restrict__ topk_w,
+                                            const T* __restrict__ h, T* __restrict__ out, int n_tokens, int hidden, int top) {
+  pdl_trigger();
+  pdl_wait();
+  const int n = blockIdx.x;
+  __shared__ int rows[MOE_MAX_TOP];
+  __shared__ float ws[MOE_MAX_TOP];
+  if (threadIdx.x < top) {
+    rows[threadIdx.x] = pair_row[(size_t)n * top + threadIdx.x];
+    ws[threadIdx.x] = topk_w[(size_t)n * top + threadIdx.x];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const float v = rows[k] >= 0 ? y[(size_t)rows[k] * hidden + c] : to_f32(h[(size_t)n * hidden + c]);
+      acc = fmaf(ws[k], v, acc);
+    }
+    out[(size_t)n * hidden + c] = from_f32<T>(acc);
+  }
+}
+
 // Rows that the sorted pairs can take at most: every pair, and each expert filled up to a tile.
 Q25_EXPORT int q25_moe_max_rows(int n_pairs, int experts, int tile) {
   const int most_tiles = (n_pairs + tile - 1) / tile + experts;
@@ -481,32 +577,32 @@ Q25_EXPORT int q25_moe_sort(const int* topk_idx, const int* counts, int* cursor,
   const int max_rows = q25_moe_max_rows(n_pairs, experts, tile);
   launch(moe_plan_kernel, dim3(1), dim3(256), 0, (cudaStream_t)stream, counts, plan, row_pair, experts, tile, max_rows);
   launch(moe_scatter_kernel, dim3((n_pairs + 255) / 256), dim3(256), 0, (cudaStream_t)stream, topk_idx, (const int*)plan, cursor, row_pair,
-         pair_row, n_pairs);
+         pair_row, n_pairs, experts);
   return launch_status();
 }
 
 template <bool GATE_UP, int BM, int WARPS_M, int STAGES>
 static int moe_grouped_mma_shape(const void* A, const void* W0, const void* W1, void* out, const int* plan, const int* row_pair,
-                                 int tiles, int experts, int N, int K, long long w_stride, float limit, float alpha, cudaStream_t s) {
+                                 int tiles, int experts, int N, int K, long long w_stride, float limit, float alpha, float shift, cudaStream_t s) {
   constexpr int SMEM = STAGES * (BM + (GATE_UP ? 128 : 64)) * (64 * 2 + 16);
   const cudaError_t e = cudaFuncSetAttribute(moe_grouped_mma_kernel<GATE_UP, BM, WARPS_M, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
   if (e != cudaSuccess) return (int)e;
   launch(moe_grouped_mma_kernel<GATE_UP, BM, WARPS_M, STAGES>, dim3((N + 63) / 64, tiles), dim3(128), SMEM, s, (const bf16*)A, (const bf16*)W0,
-         (const bf16*)W1, out, plan, row_pair, experts, N, K, w_stride, limit, alpha);
+         (const bf16*)W1, out, plan, row_pair, experts, N, K, w_stride, limit, alpha, shift);
   return launch_status();
 }
 
 // A: the rows in the sorted order, [rows, K] bfloat16.
 template <bool GATE_UP>
 static int moe_grouped_mma(const void* A, const void* W0, const void* W1, void* out, const int* plan, const int* row_pair,
-                           int n_pairs, int experts, int N, int K, long long w_stride, float limit, float alpha, int tile, void* stream) {
+                           int n_pairs, int experts, int N, int K, long long w_stride, float limit, float alpha, float shift, int tile, void* stream) {
   const int tiles = q25_moe_max_rows(n_pairs, experts, tile) / tile;
   cudaStream_t s = (cudaStream_t)stream;
-  if (tile == 16) return moe_grouped_mma_shape<GATE_UP, 16, 1, 4>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, w_stride, limit, alpha, s);
+  if (tile == 16) return moe_grouped_mma_shape<GATE_UP, 16, 1, 4>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, w_stride, limit, alpha, shift, s);
   // two stages for the large tiles: three or four CTAs then share an SM (12 to 16 warps), which hides the fixed latencies between
   // a fragment's load and its products better than a third stage does (gate and up at 4,096 rows: 268 us with three stages)
-  if (tile == 64) return moe_grouped_mma_shape<GATE_UP, 64, 2, 2>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, w_stride, limit, alpha, s);
-  if (tile == 128) return moe_grouped_mma_shape<GATE_UP, 128, 4, 2>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, w_stride, limit, alpha, s);
+  if (tile == 64) return moe_grouped_mma_shape<GATE_UP, 64, 2, 2>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, w_stride, limit, alpha, shift, s);
+  if (tile == 128) return moe_grouped_mma_shape<GATE_UP, 128, 4, 2>(A, W0, W1, out, plan, row_pair, tiles, experts, N, K, w_stride, limit, alpha, shift, s);
   return (int)cudaErrorInvalidValue;
 }
 
@@ -517,18 +613,18 @@ static bool moe_mma_takes(const void* A, const void* W0, const void* W1, const v
 template <typename T, bool GATE_UP>
 static int moe_grouped_fma(const void* A, const void* W0, const void* W1, void* out, const int* plan, const int* row_pair,
                            const float* topk_w, int n_pairs, int experts, int top, int N, int K, long long w_stride, float limit,
-                           float alpha, int tile, void* stream) {
+                           float alpha, float shift, int tile, void* stream) {
   if (n_pairs <= 0) return 0;
   const int tiles = q25_moe_max_rows(n_pairs, experts, tile) / tile;
   if (tile == 16) {
     launch(moe_grouped_fma_kernel<T, GATE_UP, 16, 64, 16, 1, 4>, dim3((N + 63) / 64, tiles), dim3(256), 0, (cudaStream_t)stream,
-           (const T*)A, (const T*)W0, (const T*)W1, out, plan, row_pair, topk_w, experts, top, N, K, w_stride, limit, alpha);
+           (const T*)A, (const T*)W0, (const T*)W1, out, plan, row_pair, topk_w, experts, top, N, K, w_stride, limit, alpha, shift);
   } else if (tile == 64) {
     launch(moe_grouped_fma_kernel<T, GATE_UP, 64, 64, 16, 4, 4>, dim3((N + 63) / 64, tiles), dim3(256), 0, (cudaStream_t)stream,
-           (const T*)A, (const T*)W0, (const T*)W1, out, plan, row_pair, topk_w, experts, top, N, K, w_stride, limit, alpha);
+           (const T*)A, (const T*)W0, (const T*)W1, out, plan, row_pair, topk_w, experts, top, N, K, w_stride, limit, alpha, shift);
   } else if (tile == 128) {     // the rows were laid out for the tensor-core product, which then did not take the operands
     launch(moe_grouped_fma_kernel<T, GATE_UP, 128, 64, 16, 8, 4>, dim3((N + 63) / 64, tiles), dim3(256), 0, (cudaStream_t)stream,
-           (const T*)A, (const T*)W0, (const T*)W1, out, plan, row_pair, topk_w, experts, top, N, K, w_stride, limit, alpha);
+           (const T*)A, (const T*)W0, (const T*)W1, out, plan, row_pair, topk_w, experts, top, N, K, w_stride, limit, alpha, shift);
   } else {
     return (int)cudaErrorInvalidValue;
   }
@@ -540,10 +636,10 @@ static int moe_grouped_fma(const void* A, const void* W0, const void* W1, void* 
 // order (bfloat16: the tensor-core product reads them; nullptr or float: the product gathers by itself).
 Q25_EXPORT int q25_moe_gate_up_f32(const void* h, const void* wgu, void* act, const int* plan, const int* row_pair,
                                    const float* topk_w, int n_pairs, int experts, int top, int ff, int hidden, float limit,
-                                   float alpha, int tile, void* sorted, void* s) {
+                                   float alpha, float shift, int tile, void* sorted, void* s) {
   const float* w = (const float*)wgu;
   return moe_grouped_fma<float, true>(h, w, w + (size_t)ff * hidden, act, plan, row_pair, topk_w, n_pairs, experts, top, ff, hidden,
-                                      2LL * ff * hidden, limit, alpha, tile, s);
+                                      2LL * ff * hidden, limit, alpha, shift, tile, s);
 }
 Q25_EXPORT int q25_moe_gather_bf16(const void* h, const int* row_pair, const float* topk_w, void* sorted, int rows, int top, int hidden,
                                    void* s) {
@@ -554,30 +650,30 @@ Q25_EXPORT int q25_moe_gather_bf16(const void* h, const int* row_pair, const flo
 }
 Q25_EXPORT int q25_moe_gate_up_bf16(const void* h, const void* wgu, void* act, const int* plan, const int* row_pair,
                                     const float* topk_w, int n_pairs, int experts, int top, int ff, int hidden, float limit,
-                                    float alpha, int tile, void* sorted, void* s) {
+                                    float alpha, float shift, int tile, void* sorted, void* s) {
   if (n_pairs <= 0) return 0;
   const bf16* w = (const bf16*)wgu;
   const bf16* wu = w + (size_t)ff * hidden;
   if (sorted && moe_mma_takes(h, w, wu, sorted, hidden)) {
     launch(moe_gather_kernel, dim3(q25_moe_max_rows(n_pairs, experts, tile)), dim3(128), 0, (cudaStream_t)s, (const bf16*)h, row_pair, topk_w,
            (bf16*)sorted, top, hidden);
-    return moe_grouped_mma<true>(sorted, w, wu, act, plan, row_pair, n_pairs, experts, ff, hidden, 2LL * ff * hidden, limit, alpha, tile, s);
+    return moe_grouped_mma<true>(sorted, w, wu, act, plan, row_pair, n_pairs, experts, ff, hidden, 2LL * ff * hidden, limit, alpha, shift, tile, s);
   }
-  return moe_grouped_fma<bf16, true>(h, w, wu, act, plan, row_pair, topk_w, n_pairs, experts, top, ff, hidden, 2LL * ff * hidden, limit, alpha,
+  return moe_grouped_fma<bf16, true>(h, w, wu, act, plan, row_pair, topk_w, n_pairs, experts, top, ff, hidden, 2LL * ff * hidden, limit, alpha, shift,
                                      tile, s);
 }
 Q25_EXPORT int q25_moe_down_f32(const void* act, const void* wd, void* y, const int* plan, const int* row_pair, int n_pairs,
                                 int experts, int top, int hidden, int ff, int tile, void* s) {
   return moe_grouped_fma<float, false>(act, wd, nullptr, y, plan, row_pair, nullptr, n_pairs, experts, top, hidden, ff, (long long)hidden * ff,
-                                       0.f, 0.f, tile, s);
+                                       0.f, 0.f, 0.f, tile, s);
 }
 Q25_EXPORT int q25_moe_down_bf16(const void* act, const void* wd, void* y, const int* plan, const int* row_pair, int n_pairs,
                                  int experts, int top, int hidden, int ff, int tile, void* s) {
   if (n_pairs <= 0) return 0;
   if (moe_mma_takes(act, wd, nullptr, nullptr, ff))
-    return moe_grouped_mma<false>(act, wd, nullptr, y, plan, row_pair, n_pairs, experts, hidden, ff, (long long)hidden * ff, 0.f, 0.f, tile, s);
+    return moe_grouped_mma<false>(act, wd, nullptr, y, plan, row_pair, n_pairs, experts, hidden, ff, (long long)hidden * ff, 0.f, 0.f, 0.f, tile, s);
   return moe_grouped_fma<bf16, false>(act, wd, nullptr, y, plan, row_pair, nullptr, n_pairs, experts, top, hidden, ff, (long long)hidden * ff,
-                                      0.f, 0.f, tile, s);
+                                      0.f, 0.f, 0.f, tile, s);
 }
 
 template <typename T>
@@ -593,4 +689,56 @@ Q25_EXPORT int q25_moe_combine_f32(const float* y, const int* pr, const float* s
 }
 Q25_EXPORT int q25_moe_combine_bf16(const float* y, const int* pr, const float* sg, const void* sh, void* out, int n, int h, int top, void* s) {
   return moe_combine<bf16>(y, pr, sg, sh, out, n, h, top, s);
+}
+
+template <typename T, int TOK>
+static int moe_route_softmax_shape(const void* h, const float* router, const float* correction, int* topk_idx, float* topk_w, int* counts,
+                                   int n_tokens, int hidden, int experts, int outputs, int top, int groups, int keep, cudaStream_t stream) {
+  const size_t smem = (size_t)TOK * (((hidden + 3) & ~3) + 3 * (MOE_MAX_EXPERTS + 1)) * sizeof(float);
+  if (smem > 200 * 1024) return -1;
+  if (smem > 48 * 1024) {
+    const cudaError_t e = cudaFuncSetAttribute(moe_route_softmax_kernel<T, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  launch(moe_route_softmax_kernel<T, TOK>, dim3((n_tokens + TOK - 1) / TOK), dim3(256), smem, stream, (const T*)h, router, correction,
+         topk_idx, topk_w, counts, n_tokens, hidden, experts, outputs, top, groups, keep);
+  return launch_status();
+}
+
+template <typename T>
+static int moe_route_softmax(const void* h, const float* router, const float* correction, int* topk_idx, float* topk_w, int* counts,
+                             int n_tokens, int hidden, int experts, int outputs, int top, int groups, int keep, void* stream) {
+  if (n_tokens <= 0) return 0;
+  if (experts <= 0 || outputs < experts || outputs > MOE_MAX_EXPERTS || top <= 0 || top > MOE_MAX_TOP || groups < 1 || outputs % groups ||
+      keep < 1 || keep > groups || top > keep * (outputs / groups))
+    return (int)cudaErrorInvalidValue;
+  cudaStream_t s = (cudaStream_t)stream;
+  int rc = -1;
+  if (n_tokens >= 512) rc = moe_route_softmax_shape<T, 4>(h, router, correction, topk_idx, topk_w, counts, n_tokens, hidden, experts, outputs, top, groups, keep, s);
+  if (rc == -1) rc = moe_route_softmax_shape<T, 1>(h, router, correction, topk_idx, topk_w, counts, n_tokens, hidden, experts, outputs, top, groups, keep, s);
+  return rc == -1 ? (int)cudaErrorInvalidValue : rc;
+}
+Q25_EXPORT int q25_moe_route_softmax_f32(const void* h, const float* r, const float* corr, int* ti, float* tw, int* counts, int n, int hidden,
+                                         int experts, int outputs, int top, int groups, int keep, void* s) {
+  return moe_route_softmax<float>(h, r, corr, ti, tw, counts, n, hidden, experts, outputs, top, groups, keep, s);
+}
+Q25_EXPORT int q25_moe_route_softmax_bf16(const void* h, const float* r, const float* corr, int* ti, float* tw, int* counts, int n, int hidden,
+                                          int experts, int outputs, int top, int groups, int keep, void* s) {
+  return moe_route_softmax<bf16>(h, r, corr, ti, tw, counts, n, hidden, experts, outputs, top, groups, keep, s);
+}
+
+template <typename T>
+static int moe_combine_weighted(const float* y, const int* pair_row, const float* topk_w, const void* h, void* out, int n_tokens, int hidden,
+                                int top, void* stream) {
+  if (n_tokens <= 0) return 0;
+  if (top > MOE_MAX_TOP) return (int)cudaErrorInvalidValue;
+  launch(moe_combine_weighted_kernel<T>, dim3(n_tokens), dim3(hidden >= 2048 ? 256 : 128), 0, (cudaStream_t)stream, y, pair_row, topk_w,
+         (const T*)h, (T*)out, n_tokens, hidden, top);
+  return launch_status();
+}
+Q25_EXPORT int q25_moe_combine_weighted_f32(const float* y, const int* pr, const float* tw, const void* h, void* out, int n, int hd, int top, void* s) {
+  return moe_combine_weighted<float>(y, pr, tw, h, out, n, hd, top, s);
+}
+Q25_EXPORT int q25_moe_combine_weighted_bf16(const float* y, const int* pr, const float* tw, const void* h, void* out, int n, int hd, int top, void* s) {
+  return moe_combine_weighted<bf16>(y, pr, tw, h, out, n, hd, top, s);
 }

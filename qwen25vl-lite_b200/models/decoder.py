@@ -27,6 +27,7 @@ class StopRuntime:
     cache_of: Optional[int]
     owns_cache: bool
     state: Optional[torch.Tensor] = None     # [max_requests, *shape], set by the runner
+    enters: Optional[int] = None             # the pass that begins here: the model's reentry part runs first
 
 
 class DecoderModel:
@@ -57,7 +58,11 @@ class DecoderModel:
         self.head = parts.build_part(parts.HEADS, spec.head, "output head")
         self._named_parts.append((spec.final_norm.prefix, self.final_norm))
         self._named_parts.append((spec.head.prefix, self.head))
-        self.stops = [StopRuntime(i, s.layer, s.cache_of, s.cache_of is None) for i, s in enumerate(spec.schedule)]
+        self.reentry = None
+        if spec.reentry is not None:
+            self.reentry = parts.build_part(parts.STREAM_PARTS, spec.reentry, "stream part")
+            self._named_parts.append((spec.reentry.prefix, self.reentry))
+        self.stops = [StopRuntime(i, s.layer, s.cache_of, s.cache_of is None, enters=s.enters) for i, s in enumerate(spec.schedule)]
         self.dtype: Optional[torch.dtype] = None
         self.device = None
 
@@ -76,7 +81,16 @@ class DecoderModel:
 
     def planning_parts(self) -> List[parts.Part]:
         """The parts whose kernels read work lists that the step function packs (``plan_step``)."""
-        return [part for _, part in self._named_parts if part.plan_key() is not None]
+        return [part for part in self._all_parts() if part.plan_key() is not None]
+
+    def _all_parts(self) -> List[parts.Part]:
+        """The model's parts and the parts they are made of."""
+        out, todo = [], [part for _, part in self._named_parts]
+        while todo:
+            part = todo.pop(0)
+            out.append(part)
+            todo = list(part.sub_parts()) + todo
+        return out
 
     # ---- weights -----------------------------------------------------------------------
     def expected_tensors(self) -> Dict[str, parts.TensorSpec]:
@@ -108,7 +122,7 @@ class DecoderModel:
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0
-        for _, part in self._named_parts:
+        for part in self._all_parts():
             for v in vars(part).values():
                 for t in (v.weight, v.bias) if hasattr(v, "weight") and hasattr(v, "bias") else (v,):
                     if isinstance(t, torch.Tensor) and t.data_ptr() not in seen:
@@ -125,14 +139,32 @@ class DecoderModel:
         return out
 
     # ---- forward -----------------------------------------------------------------------
+    @staticmethod
+    def _add_pending(ctx, x, pending) -> None:
+        """Adds an update that no norm is about to add (the stream is read as it is next)."""
+        if pending is None:
+            return
+        if isinstance(pending, parts.PendingUpdate):
+            if not hasattr(pending.norm, "add_only"):
+                raise TypeError(f"a {type(pending.norm).__name__} cannot add a pending update without normalising for a next sublayer")
+            pending.norm.add_only(ctx, x, pending.value)
+        else:
+            x.add_(pending)
+
     def forward(self, ctx) -> Optional[torch.Tensor]:
         """Runs the step described by ``ctx`` and returns float32 logits [wanted, vocab]
         (None when nothing is wanted)."""
         if hasattr(ctx, "shared"):
             ctx.shared.clear()
         x = self.embedding.forward(ctx)
+        if self.reentry is not None:
+            self.reentry.remember(ctx, x)
         pending = None
         for stop in self.stops:
+            if stop.enters is not None:
+                self._add_pending(ctx, x, pending)
+                pending = None
+                self.reentry.forward(ctx, x, stop.enters)
             pending = self.blocks[stop.layer].forward(ctx, x, pending, stop)
         if ctx.logit_rows is None or ctx.logit_rows.shape[0] == 0:
             return None

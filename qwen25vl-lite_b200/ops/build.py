@@ -33,7 +33,7 @@ NVCC_FLAGS = [
 # serving path of rotary softmax attention loads; "recurrent", "biased" and "routed" the kernels of the gated linear recurrence,
 # of attention with a distance bias, kept first tokens or a sink, and of the routed feed-forward; "rotary" a
 # rotation of part of a head in either pairing, "latent" the compressed cache row of latent attention,
-# "retention" the decayed linear attention.  A
+# "retention" the decayed linear attention, "memory" the matrix memories whose gates depend on the token.  A
 # library is compiled when a model first asks for one of its kernels, so a run compiles only what
 # its model and dtype need.
 LIBRARIES: Dict[str, List[str]] = {
@@ -47,6 +47,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "rotary": ["rotary.cu"],
     "latent": ["latent.cu"],
     "retention": ["retention.cu"],
+    "memory": ["gated_memory.cu"],
 }
 
 

@@ -21,26 +21,36 @@ _F = ctypes.c_float
 _LL = ctypes.c_longlong
 
 _SIGNATURES = {
-    "q25_embed_gather": [_P, _P, _P, _I, _I, _I, _P],
+    "q25_embed_gather": [_P, _P, _P, _I, _I, _I, _F, _P],
     "q25_add_rmsnorm": [_P, _P, _P, _F, _P, _P, _I, _I, _P],
     "q25_silu_mul": [_P, _P, _I, _I, _I, _P],
     "q25_rope_store": [_P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "q25_paged_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     "q25_embed_position_norm": [_P, _P, _P, _P, _P, _F, _P, _I, _I, _I, _I, _I, _P],
     "q25_add_norm_groups": [_P, _P, _P, _F, _I, _P, _F, _I, _P, _P, _I, _I, _P],
-    "q25_glu_clamped": [_P, _P, _I, _I, _F, _F, _I, _P],
+    "q25_glu_clamped": [_P, _P, _I, _I, _F, _F, _F, _I, _P],
     "q25_rglru_conv": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "q25_rglru_scan": [_P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _I, _I, _P],
-    "q25_biased_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _I, _P],
+    "q25_biased_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _I, _F, _P],
+    "q25_biased_attention_qk_norm_store": [_P, _I, _P, _P, _F, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "q25_add_dyt": [_P, _P, _P, _P, _F, _P, _P, _I, _I, _P],
     "q25_rotary_apply": [_P, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "q25_latent_store": [_P, _I, _I, _I, _P, _F, _P, _I, _I, _P, _P, _I, _P],
     "q25_retention": [_P, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _P, _I, _P, _I, _P, _I, _I, _P],
     "q25_kv_store_mix": [_P, _I, _P, _I, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "q25_moe_route": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
-    "q25_moe_gate_up": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
+    "q25_moe_gate_up": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _F, _I, _P, _P],
     "q25_moe_down": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "q25_moe_combine": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "q25_moe_route_softmax": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "q25_moe_combine_weighted": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "q25_add_layernorm": [_P, _P, _P, _P, _P, _F, _P, _P, _F, _P, _P, _I, _I, _P],
+    "q25_branch_mean_norm": [_P, _P, _I, _P, _I, _I, _F, _P],
+    "q25_stream_pair": [_P, _P, _P, _I, _I, _P],
+    "q25_memory_gla_decay": [_P, _I, _I, _I, _P, _P, _F, _P, _I, _I, _P],
+    "q25_memory_row_dots": [_P, _P, _P, _P, _I, _I, _I, _P],
+    "q25_memory_scan": [_P, _I, _I, _I, _I, _P, _P, _F, _F, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "q25_memory_output": [_P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _I, _P],
 }
 _UNTYPED = {
     "q25_attention_decode_bf16": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
@@ -78,7 +88,7 @@ def load_library(name: str = "core") -> ctypes.CDLL:
 _SYMBOL_LIBRARY = (("q25_gemm_chain", "chain"), ("q25_attention_decode", "bf16"), ("q25_attention_prefill", "bf16"),
                    ("q25_gemm_tcgen05", "tcgen05"), ("q25_rope_angles", "bf16"), ("q25_rglru", "recurrent"),
                    ("q25_biased_attention", "biased"), ("q25_kv_store_mix", "biased"), ("q25_moe", "routed"),
-                   ("q25_rotary", "rotary"), ("q25_latent", "latent"), ("q25_retention", "retention"))
+                   ("q25_rotary", "rotary"), ("q25_latent", "latent"), ("q25_retention", "retention"), ("q25_memory", "memory"))
 
 
 def _library_of(symbol: str) -> str:
@@ -170,12 +180,12 @@ def _dev(t: torch.Tensor, dtype: torch.dtype, what: str) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------------
 
 
-def embed_gather(table: torch.Tensor, ids: torch.Tensor, x_out: torch.Tensor) -> None:
-    """x_out[n, :] (float32) = table[ids[n], :]."""
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, x_out: torch.Tensor, scale: float = 1.0) -> None:
+    """x_out[n, :] (float32) = table[ids[n], :] * scale."""
     n, hidden = x_out.shape
     _dev(ids, torch.int32, "embed_gather ids"); _dev(x_out, torch.float32, "embed_gather out")
     _check(_typed("q25_embed_gather", table.dtype)(table.data_ptr(), ids.data_ptr(), x_out.data_ptr(), n, hidden,
-                                                   table.shape[0], _stream()), "embed_gather")
+                                                   table.shape[0], float(scale), _stream()), "embed_gather")
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
@@ -667,13 +677,14 @@ def add_norm_groups(x: torch.Tensor, delta: Optional[torch.Tensor], delta_weight
         _ptr(out), _ptr(rows), n_out, hidden, _stream()), "add_norm_groups")
 
 
-def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float, paired: bool = False) -> None:
-    """out = g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit);
+def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float, paired: bool = False, shift: float = 1.0) -> None:
+    """out = g * sigmoid(alpha g) * (u + shift), g = min(gate, limit), u = clamp(up, -limit, limit) (an infinite
+    limit, alpha 1 and shift 0: silu(gate) * up);
     ``gate_up`` rows hold the gate features, then the up features, or with ``paired`` groups of 8 gate
     features followed by their 8 up features."""
     n, inter = out.shape
     _dev(gate_up, out.dtype, "glu_clamped input")
-    _check(_typed("q25_glu_clamped", out.dtype)(gate_up.data_ptr(), out.data_ptr(), n, inter, float(limit), float(alpha), int(paired),
+    _check(_typed("q25_glu_clamped", out.dtype)(gate_up.data_ptr(), out.data_ptr(), n, inter, float(limit), float(alpha), float(shift), int(paired),
                                                 _stream()), "glu_clamped")
 
 
@@ -745,10 +756,11 @@ def biased_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torc
                              block_table: torch.Tensor, token_seq: torch.Tensor, cu_q: torch.Tensor, q_start_pos: torch.Tensor,
                              nq: int, nkv: int, dk: int, dv: int, page_size: int, window: int, keep_first: int, scale: float,
                              r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], sink: Optional[torch.Tensor] = None,
-                             v_row: int = 0) -> None:
+                             v_row: int = 0, softcap: float = 0.0) -> None:
     """``sink`` (float32 [nq]): a score per query head that has no key and no value and joins the
     softmax's denominator.  ``v_row``: channels between two value rows of a page when the values lie
-    inside the key rows (0: the values have pages of their own, rows of ``dv`` channels)."""
+    inside the key rows (0: the values have pages of their own, rows of ``dv`` channels).  ``softcap`` c > 0:
+    the scaled score becomes ``c * tanh(score / c)`` before anything else is added to it."""
     if sink is not None:
         _dev(sink, torch.float32, "attention sink")
     if dv > 512:
@@ -756,8 +768,8 @@ def biased_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torc
     _check(_typed("q25_biased_attention_generic", qkv.dtype)(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], token_seq.data_ptr(), cu_q.data_ptr(), q_start_pos.data_ptr(), qkv.shape[0], nq, nkv, dk, dv,
-        page_size, int(window or 0), int(keep_first or 0), float(scale), _ptr(r1), _ptr(r2), _ptr(sink), int(v_row or 0), _stream()),
-        "biased_attention_generic")
+        page_size, int(window or 0), int(keep_first or 0), float(scale), _ptr(r1), _ptr(r2), _ptr(sink), int(v_row or 0), float(softcap or 0.0),
+        _stream()), "biased_attention_generic")
 
 
 # rows of a latent cache the tensor-core kernels are also built for: (rank + rotated channels, rank)
@@ -773,7 +785,8 @@ def biased_attention_mma(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
                          cu_q: torch.Tensor, q_start_pos: torch.Tensor, tiles: Optional[torch.Tensor], items: Optional[torch.Tensor],
                          nq: int, nkv: int, dk: int, dv: int, page_size: int, window: int, keep_first: int, scale: float,
                          r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], n_splits: int = 1,
-                         scratch: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None, v_row: int = 0) -> None:
+                         scratch: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None, v_row: int = 0,
+                         softcap: float = 0.0) -> None:
     """Tensor-core attention (bfloat16): ``tiles`` int32 [n, 2] are (entry, tile of 64 (token, head of
     the group) rows) of the runs, ``items`` the entries that bring one token, whose keys are cut into
     ``n_splits`` ranges (partial results through ``scratch``, float32, len(items) * nq * n_splits * (dv + 2))."""
@@ -789,11 +802,11 @@ def biased_attention_mma(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
     if not biased_attention_mma_supports(qkv.dtype, dk, dv) or (n_items and nq // nkv > 16):
         raise KernelError(f"biased_attention_mma: unsupported sizes {dk}/{dv} or more than 16 heads per kv head for single tokens")
     _check(_fn("q25_biased_attention_mma_bf16",
-               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _I, _I, _P, _P, _P])(
+               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _I, _I, _P, _P, _F, _P])(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], cu_q.data_ptr(), q_start_pos.data_ptr(), _ptr(tiles), n_tiles, _ptr(items), n_items, nq, nkv, dk, dv,
         page_size, int(window or 0), int(keep_first or 0), float(scale), _ptr(r1), _ptr(r2), _ptr(sink), int(v_row or 0), int(n_splits),
-        part_o, part_ml, _stream()), "biased_attention_mma")
+        part_o, part_ml, float(softcap or 0.0), _stream()), "biased_attention_mma")
     count_replayed((1 if n_tiles and n_items else 0) + (1 if n_items and n_splits > 1 else 0))
 
 
@@ -942,26 +955,30 @@ def moe_sort(topk_idx: torch.Tensor, counts: torch.Tensor, cursor: torch.Tensor,
 
 
 def moe_gate_up(h: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, plan: torch.Tensor, row_pair: torch.Tensor,
-                topk_w: torch.Tensor, top: int, limit: float, alpha: float, tile: int) -> None:
+                topk_w: Optional[torch.Tensor], top: int, limit: float, alpha: float, tile: int, shift: float = 1.0,
+                n_pairs: Optional[int] = None) -> None:
     """act[row] = glu(expert of the row's tile applied to weight * h[token of the row]) for the sorted
-    rows.  ``w_gate_up``: [experts, 2 * ff, hidden], an expert's gate rows and then its up rows."""
+    rows.  ``w_gate_up``: [experts, 2 * ff, hidden], an expert's gate rows and then its up rows.  Without
+    ``topk_w`` the rows go in as they are (``n_pairs`` then says how many pairs the step has); ``shift`` as for
+    ``glu_clamped``."""
+    n_pairs = topk_w.numel() if n_pairs is None else int(n_pairs)
     experts, ff2, hidden = w_gate_up.shape
     _dev(h, act.dtype, "moe_gate_up input")
     _dev(w_gate_up, h.dtype, "moe_gate_up weights"); _dev(act, h.dtype, "moe_gate_up act")
     # bfloat16: the rows are first written out in the sorted order, weighted, for the tensor-core product
     sorted_rows = torch.empty((act.shape[0], hidden), dtype=h.dtype, device=h.device) if h.dtype == torch.bfloat16 else None
     _check(_typed("q25_moe_gate_up", h.dtype)(h.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), plan.data_ptr(),
-                                              row_pair.data_ptr(), topk_w.data_ptr(), topk_w.numel(), experts, int(top), ff2 // 2, hidden,
-                                              float(limit), float(alpha), int(tile), _ptr(sorted_rows), _stream()), "moe_gate_up")
+                                              row_pair.data_ptr(), _ptr(topk_w), n_pairs, experts, int(top), ff2 // 2, hidden,
+                                              float(limit), float(alpha), float(shift), int(tile), _ptr(sorted_rows), _stream()), "moe_gate_up")
     if sorted_rows is not None:
         count_replayed(1)
 
 
-def moe_gather(h: torch.Tensor, row_pair: torch.Tensor, topk_w: torch.Tensor, top: int, sorted_rows: torch.Tensor) -> None:
+def moe_gather(h: torch.Tensor, row_pair: torch.Tensor, topk_w: Optional[torch.Tensor], top: int, sorted_rows: torch.Tensor) -> None:
     """sorted_rows[row] = weight of the row's pair * h[token of the pair] (bfloat16), the input of the grouped products."""
     _dev(h, torch.bfloat16, "moe_gather input"); _dev(sorted_rows, torch.bfloat16, "moe_gather rows")
     _check(_fn("q25_moe_gather_bf16", [_P, _P, _P, _P, _I, _I, _I, _P])(
-        h.data_ptr(), row_pair.data_ptr(), topk_w.data_ptr(), sorted_rows.data_ptr(), sorted_rows.shape[0], int(top), h.shape[1],
+        h.data_ptr(), row_pair.data_ptr(), _ptr(topk_w), sorted_rows.data_ptr(), sorted_rows.shape[0], int(top), h.shape[1],
         _stream()), "moe_gather")
 
 
@@ -1002,3 +1019,161 @@ def moe_combine(y: torch.Tensor, pair_row: torch.Tensor, sg: Optional[torch.Tens
         _dev(shared, out.dtype, "moe_combine shared")
     _check(_typed("q25_moe_combine", out.dtype)(y.data_ptr(), pair_row.data_ptr(), _ptr(sg), _ptr(shared), out.data_ptr(), n, hidden,
                                                 int(top), _stream()), "moe_combine")
+
+
+def moe_route_softmax(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], experts: int, top: int, groups: int,
+                      keep: int, topk_idx: torch.Tensor, topk_w: torch.Tensor, counts: torch.Tensor) -> None:
+    """Router logits in float32 over all rows of ``router`` (the last ``rows - experts`` stand for experts without
+    matrices), scores = softmax; the ``top`` largest of score + correction inside the ``keep`` best of ``groups``
+    equal runs of rows are chosen and weigh in with their plain scores; ``counts`` (one per expert with matrices)
+    takes how many tokens chose each."""
+    n, hidden = h.shape
+    outputs = router.shape[0]
+    _dev(router, torch.float32, "moe_route_softmax router"); _dev(topk_idx, torch.int32, "moe_route_softmax idx")
+    _dev(topk_w, torch.float32, "moe_route_softmax weights"); _dev(counts, torch.int32, "moe_route_softmax counts")
+    if correction is not None:
+        _dev(correction, torch.float32, "moe_route_softmax correction")
+    _check(_typed("q25_moe_route_softmax", h.dtype)(h.data_ptr(), router.data_ptr(), _ptr(correction), topk_idx.data_ptr(), topk_w.data_ptr(),
+                                                    counts.data_ptr(), n, hidden, int(experts), outputs, int(top), int(groups), int(keep),
+                                                    _stream()), "moe_route_softmax")
+
+
+def moe_combine_weighted(y: torch.Tensor, pair_row: torch.Tensor, topk_w: torch.Tensor, h: torch.Tensor, out: torch.Tensor, top: int) -> None:
+    """out[n] = sum over the token's choices of weight * (the row of ``y`` the choice has, or h[n] itself when it has none)."""
+    n, hidden = out.shape
+    _dev(y, torch.float32, "moe_combine_weighted rows"); _dev(h, out.dtype, "moe_combine_weighted input")
+    _check(_typed("q25_moe_combine_weighted", out.dtype)(y.data_ptr(), pair_row.data_ptr(), topk_w.data_ptr(), h.data_ptr(), out.data_ptr(),
+                                                         n, hidden, int(top), _stream()), "moe_combine_weighted")
+
+
+# ---- layer norm around the residual stream, branches into one update, a stream mixed with another ---------
+
+
+def add_layernorm(x: torch.Tensor, delta: Optional[torch.Tensor], delta_weight: Optional[torch.Tensor], delta_bias: Optional[torch.Tensor],
+                  delta_scale: Optional[torch.Tensor], delta_eps: float, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+                  eps: float, out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None, dtype: Optional[torch.dtype] = None) -> None:
+    """x += post(delta); out = layer_norm(x) * weight + bias.  post(delta) is the layer norm of the update with
+    ``delta_weight`` and ``delta_bias``, times ``delta_scale`` per channel when given; without a weight the update
+    goes in as it is.  ``out`` None: only the addition.  ``rows`` as for ``add_rmsnorm``."""
+    hidden = x.shape[-1]
+    dtype = out.dtype if out is not None else (delta.dtype if delta is not None else dtype)
+    _dev(x, torch.float32, "add_layernorm x")
+    for t in (delta_weight, delta_bias, delta_scale, weight, bias):
+        if t is not None:
+            _dev(t, torch.float32, "add_layernorm weight")
+    if delta is not None:
+        _dev(delta, dtype, "add_layernorm delta")
+    if rows is not None:
+        _dev(rows, torch.int32, "add_layernorm rows")
+    n_out = out.shape[0] if out is not None else x.shape[0]
+    _check(_typed("q25_add_layernorm", dtype)(x.data_ptr(), _ptr(delta), _ptr(delta_weight), _ptr(delta_bias), _ptr(delta_scale),
+                                              float(delta_eps), _ptr(weight), _ptr(bias), float(eps), _ptr(out), _ptr(rows), n_out, hidden,
+                                              _stream()), "add_layernorm")
+
+
+def branch_mean_norm(branches, weights, eps: float, out: torch.Tensor) -> None:
+    """out = mean over the branches of branch / rms(branch) * weight (up to 4 branches of out's shape and dtype)."""
+    n = len(branches)
+    if not 1 <= n <= 4 or len(weights) != n:
+        raise KernelError("branch_mean_norm: 1 to 4 branches, each with a weight")
+    for b, w in zip(branches, weights):
+        _dev(b, out.dtype, "branch_mean_norm branch"); _dev(w, torch.float32, "branch_mean_norm weight")
+        if b.shape != out.shape:
+            raise KernelError("branch_mean_norm: branches and result have one shape")
+    ins = (ctypes.c_void_p * 4)(*[b.data_ptr() for b in branches], *([None] * (4 - n)))
+    ws = (ctypes.c_void_p * 4)(*[w.data_ptr() for w in weights], *([None] * (4 - n)))
+    _check(_typed("q25_branch_mean_norm", out.dtype)(ctypes.addressof(ins), ctypes.addressof(ws), n, out.data_ptr(), out.shape[0], out.shape[1],
+                                                     float(eps), _stream()), "branch_mean_norm")
+
+
+def stream_pair(x: torch.Tensor, other: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n] = [x[n] | other[n]] (two float32 streams side by side) in out's dtype: the input of a product that mixes them."""
+    _dev(x, torch.float32, "stream_pair x"); _dev(other, torch.float32, "stream_pair other")
+    if out.shape != (x.shape[0], 2 * x.shape[1]) or other.shape != x.shape or not out.is_contiguous():
+        raise KernelError("stream_pair: the result holds the two streams side by side")
+    _check(_typed("q25_stream_pair", out.dtype)(x.data_ptr(), other.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1], _stream()), "stream_pair")
+
+
+def stream_set(x: torch.Tensor, y: torch.Tensor, bias: torch.Tensor) -> None:
+    """x = y + bias (float32 rows, a float32 vector), in place of what x held."""
+    _dev(x, torch.float32, "stream_set x"); _dev(y, torch.float32, "stream_set y"); _dev(bias, torch.float32, "stream_set bias")
+    if y.shape != x.shape:
+        raise KernelError("stream_set: shapes differ")
+    _check(_fn("q25_stream_set", [_P, _P, _P, _I, _I, _P])(x.data_ptr(), y.data_ptr(), bias.data_ptr(), x.shape[0], x.shape[1], _stream()),
+           "stream_set")
+
+
+# ---- queries and keys normed per head, turned, and cached; keys that serve as values --------------------
+
+
+def qk_norm_store(qk: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                  angles: Optional[torch.Tensor], layout: str, k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                  kv_slot: Optional[torch.Tensor], nq: int, nkv: int, dk: int, page_size: int, keys_as_values: bool) -> None:
+    """Rows [nq query heads | nkv key heads] of ``dk`` channels: every head divided by its root mean square and
+    multiplied by its weight (dk numbers, shared by the heads), then turned by ``angles``; queries are written back,
+    keys go to the pages at ``kv_slot``; with ``keys_as_values`` the keys as they came go to the value pages."""
+    half = 0 if angles is None else angles.shape[1]
+    if qk.stride(1) != 1:
+        raise KernelError("qk_norm_store: rows must be contiguous")
+    _check(_typed("q25_biased_attention_qk_norm_store", qk.dtype)(
+        qk.data_ptr(), qk.stride(0), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(angles), half, ROTARY_LAYOUTS[layout], _ptr(k_pages),
+        _ptr(v_pages), _ptr(kv_slot), qk.shape[0], int(nq), int(nkv), int(dk), int(page_size), int(keys_as_values), _stream()), "qk_norm_store")
+
+
+# ---- matrix memories with gates that depend on the token -------------------------------------------------
+
+
+def gla_decay(x: torch.Tensor, low_off: int, rank: int, a2t: torch.Tensor, bias: Optional[torch.Tensor], tau: float, out: torch.Tensor) -> None:
+    """out[n, c] (float32) = sigmoid(bias[c] + sum_r a2t[r, c] x[n, low_off + r]) ** (1 / tau)."""
+    _dev(a2t, torch.float32, "gla_decay factor"); _dev(out, torch.float32, "gla_decay out")
+    if a2t.shape != (rank, out.shape[1]) or x.stride(1) != 1:
+        raise KernelError("gla_decay: the second factor comes transposed, [rank, channels]")
+    _check(_typed("q25_memory_gla_decay", x.dtype)(x.data_ptr(), x.stride(0), int(low_off), int(rank), a2t.data_ptr(), _ptr(bias), float(tau),
+                                                   out.data_ptr(), x.shape[0], out.shape[1], _stream()), "gla_decay")
+
+
+def row_dots(h: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[n, j] (float32) = bias[j] + w[j] . h[n] for up to 256 float32 rows ``w``, in a fixed order of sums."""
+    _dev(h, h.dtype, "row_dots input"); _dev(w, torch.float32, "row_dots rows"); _dev(out, torch.float32, "row_dots out")
+    if w.shape[1] != h.shape[1] or out.shape != (h.shape[0], w.shape[0]) or w.shape[0] > 256:
+        raise KernelError("row_dots: up to 256 rows of the input's width")
+    _check(_typed("q25_memory_row_dots", h.dtype)(h.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), h.shape[0], h.shape[1], w.shape[0],
+                                                  _stream()), "row_dots")
+
+
+def memory_scan(x: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: Optional[torch.Tensor], gates: Optional[torch.Tensor],
+                cap: float, q_scale: float, state: torch.Tensor, cu_q: torch.Tensor, slot_ids: torch.Tensor, o_raw: torch.Tensor,
+                m_exp: Optional[torch.Tensor], n_seqs: int, heads: int, dim: int, vdim: int) -> None:
+    """Every entry's tokens in order through ``S = diag(a) S + b k v^T``, ``o = S^T q`` from the request's state, which
+    moves on.  With ``decay`` (float32 [N, heads * dim]) a is that per key channel and b = 1; the state is [slots, heads,
+    dim, vdim].  With ``gates`` (float32 [N, 2 * heads]: input gates, then forget gates, before ``cap * tanh(. / cap)``
+    and the logarithm of the forget gate's sigmoid) a and b come from the gates and a running maximum m; the state is
+    [slots, heads, dim + 1, vdim + 1] (a normaliser column, m in the last row), ``o_raw`` [N, heads, vdim + 1] ends with
+    n . q and ``m_exp`` [N, heads] takes exp(-m)."""
+    per_head = gates is not None
+    extra = 1 if per_head else 0
+    _dev(state, torch.float32, "memory_scan state"); _dev(o_raw, torch.float32, "memory_scan out")
+    if tuple(state.shape[1:]) != (heads, dim + extra, vdim + extra) or x.stride(1) != 1 or o_raw.numel() != x.shape[0] * heads * (vdim + extra):
+        raise KernelError(f"memory_scan: the state must be [slots, {heads}, {dim + extra}, {vdim + extra}]")
+    if per_head == (decay is not None):
+        raise KernelError("memory_scan: decays per channel or gates per head, one of the two")
+    _check(_typed("q25_memory_scan", x.dtype)(
+        x.data_ptr(), x.stride(0), int(q_off), int(k_off), int(v_off), _ptr(decay), _ptr(gates), float(cap), float(q_scale), state.data_ptr(),
+        cu_q.data_ptr(), slot_ids.data_ptr(), o_raw.data_ptr(), _ptr(m_exp), int(n_seqs), heads, dim, vdim, int(per_head), _stream()),
+        "memory_scan")
+
+
+MEMORY_GATES = {"silu": 0, "sigmoid": 1}
+
+
+def memory_output(o_raw: torch.Tensor, m_exp: Optional[torch.Tensor], x: torch.Tensor, g_off: int, weight: torch.Tensor, eps: float,
+                  gate: str, out: torch.Tensor, heads: int, vdim: int) -> None:
+    """out[n, head] = unit_rms(o / den) * weight * gate(x[n, g_off + head * vdim ...]); den = max(|n . q|, exp(-m)) + 1e-6
+    when ``m_exp`` is given (``o_raw`` then has one more column), else 1."""
+    extra = 0 if m_exp is None else 1
+    _dev(weight, torch.float32, "memory_output weight")
+    if weight.numel() != heads * vdim or out.shape != (x.shape[0], heads * vdim) or out.dtype != x.dtype or not out.is_contiguous():
+        raise KernelError("memory_output: a weight per channel of every head")
+    _check(_typed("q25_memory_output", x.dtype)(o_raw.data_ptr(), _ptr(m_exp), x.data_ptr(), x.stride(0), int(g_off), weight.data_ptr(),
+                                                out.data_ptr(), x.shape[0], heads, vdim, extra, float(eps), MEMORY_GATES[gate], _stream()),
+           "memory_output")

@@ -4,5 +4,5 @@ from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSI
                    KVCacheNeed, Mixer, Norm, Part, PendingUpdate, PositionEncoding, StateNeed, TensorSpec, build_part,
                    register_block, register_embedding, register_feed_forward, register_head, register_mixer,
                    register_norm, register_position_encoding)
-from . import attention, block, embedding, feed_forward, norm, position, recurrent, retention  # noqa: F401  (registration)
+from . import attention, block, composite, embedding, feed_forward, memory, norm, position, recurrent, retention, stream  # noqa: F401  (registration)
 from .position import prompt_positions  # noqa: F401

@@ -186,13 +186,21 @@ class SinkAttention(Mixer):
     has no key and no value; it is ``"learned"`` (one number per query head, the tensor ``sink``),
     ``"zero"`` (its score is 0: one is added to the denominator) or None.  The layer's position
     encoding (``position``, a ``rotary``) turns the first channels of every query and key head; values
-    are not turned.  Tensors: ``q``, ``k``, ``v``, ``o`` (and ``sink``)."""
+    are not turned.  Tensors: ``q``, ``k``, ``v``, ``o`` (and ``sink``).
+
+    Three more options.  ``softcap`` c > 0: the scaled score becomes ``c * tanh(score / c)``.
+    ``qk_norm_eps`` (a number): before the rotation every query and key head is divided by its root mean
+    square (eps inside the root) and multiplied by the weight ``q.norm`` / ``k.norm`` (``head_dim`` numbers,
+    shared by the heads).  ``values_from_keys``: there is no ``v``; a token's value is its key as projected,
+    before norm and rotation (``value_dim`` is then ``head_dim``).  With either of the last two, norm, rotation
+    and the cache write are one kernel."""
 
     graph_safe = True                # forward is a fixed sequence of this engine's kernels
     accepts_residual = True          # the output projection can add into the residual stream itself
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: Optional[int] = None,
-                 scale: Optional[float] = None, window: Optional[int] = None, sink: Optional[str] = None, position=None):
+                 scale: Optional[float] = None, window: Optional[int] = None, sink: Optional[str] = None, position=None,
+                 softcap: float = 0.0, qk_norm_eps: Optional[float] = None, values_from_keys: bool = False):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads cannot share {num_kv_heads} kv heads")
         if sink not in (None, "zero", "learned"):
@@ -201,15 +209,30 @@ class SinkAttention(Mixer):
         self.value_dim = self.head_dim if value_dim is None else int(value_dim)
         if not 0 < self.value_dim <= 512 or self.head_dim <= 0:
             raise ValueError(f"key size {head_dim} / value size {value_dim} is not supported: values take up to 512 channels")
+        self.values_from_keys = bool(values_from_keys)
+        if self.values_from_keys and self.value_dim != self.head_dim:
+            raise ValueError(f"values that are the keys have the keys' size {self.head_dim}, not {self.value_dim}")
         self.scale = float(head_dim) ** -0.5 if scale is None else float(scale)
         self.window = None if not window else int(window)
+        self.softcap = float(softcap or 0.0)
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
         self.sink_kind, self.position = sink, position
-        self.qkv_proj = self.o_proj = self.sink = None
+        if position is not None and position.dims > self.head_dim:
+            raise ValueError(f"the position encoding turns {position.dims} channels, a head has {head_dim}")
+        self.qkv_proj = self.o_proj = self.sink = self.q_norm = self.k_norm = None
+
+    @property
+    def _fused_store(self) -> bool:
+        return self.values_from_keys or self.qk_norm_eps is not None
 
     def tensor_specs(self):
         h, q = self.hidden_size, self.num_heads * self.head_dim
-        specs = [TensorSpec("q", (q, h)), TensorSpec("k", (self.num_kv_heads * self.head_dim, h)),
-                 TensorSpec("v", (self.num_kv_heads * self.value_dim, h)), TensorSpec("o", (h, self.num_heads * self.value_dim))]
+        specs = [TensorSpec("q", (q, h)), TensorSpec("k", (self.num_kv_heads * self.head_dim, h))]
+        if not self.values_from_keys:
+            specs.append(TensorSpec("v", (self.num_kv_heads * self.value_dim, h)))
+        if self.qk_norm_eps is not None:
+            specs += [TensorSpec("q.norm", (self.head_dim,), "norm"), TensorSpec("k.norm", (self.head_dim,), "norm")]
+        specs.append(TensorSpec("o", (h, self.num_heads * self.value_dim)))
         if self.sink_kind == "learned":
             specs.append(TensorSpec("sink", (self.num_heads,), "bias"))
         return tuple(specs)
@@ -218,10 +241,13 @@ class SinkAttention(Mixer):
         return KVCacheNeed(self.num_kv_heads, self.head_dim, self.window, self.value_dim)
 
     def load(self, tensors, device, dtype):
-        w = torch.cat([tensors["q"], tensors["k"], tensors["v"]], dim=0)
+        w = torch.cat([tensors["q"], tensors["k"]] + ([] if self.values_from_keys else [tensors["v"]]), dim=0)
         self.qkv_proj = Linear(w.to(device=device, dtype=dtype).contiguous())
         self.o_proj = Linear(tensors["o"].to(device=device, dtype=dtype).contiguous())
         self.sink = _sink_tensor(self.sink_kind, tensors, self.num_heads, device)
+        if self.qk_norm_eps is not None:
+            self.q_norm = tensors["q.norm"].to(device=device, dtype=torch.float32).contiguous()
+            self.k_norm = tensors["k.norm"].to(device=device, dtype=torch.float32).contiguous()
 
     def plan_key(self):
         return ("biased_window_attention", self.num_heads // self.num_kv_heads, self.window or 0, 0)
@@ -232,14 +258,24 @@ class SinkAttention(Mixer):
     def forward(self, ctx, h, stop, residual=None):
         nq, nkv, dk, dv = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim
         qkv = self.qkv_proj(h)
-        if self.position is not None:
-            qk = qkv[:, :(nq + nkv) * dk].unflatten(1, (nq + nkv, dk))       # query heads, then key heads
-            self.position.rotate(ctx, qk, qk, dk)
         kv = ctx.kv(stop)
-        if stop.owns_cache:
-            kernels.kv_store_mix(qkv, None, 0.0, kv.k_pages, kv.v_pages, kv.kv_slot, nq, nkv, dk, dv, kv.page_size)
+        if self._fused_store:
+            angles = self.position.angles(ctx) if self.position is not None else None
+            layout = self.position.layout if self.position is not None else "halves"
+            own = stop.owns_cache
+            if own and not self.values_from_keys:      # values of their own: they go first, with keys that the next kernel replaces
+                kernels.kv_store_mix(qkv, None, 0.0, kv.k_pages, kv.v_pages, kv.kv_slot, nq, nkv, dk, dv, kv.page_size)
+            kernels.qk_norm_store(qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, angles, layout, kv.k_pages if own else None,
+                                  kv.v_pages if own else None, kv.kv_slot if own else None, nq, nkv, dk, kv.page_size,
+                                  self.values_from_keys)
+        else:
+            if self.position is not None:
+                qk = qkv[:, :(nq + nkv) * dk].unflatten(1, (nq + nkv, dk))       # query heads, then key heads
+                self.position.rotate(ctx, qk, qk, dk)
+            if stop.owns_cache:
+                kernels.kv_store_mix(qkv, None, 0.0, kv.k_pages, kv.v_pages, kv.kv_slot, nq, nkv, dk, dv, kv.page_size)
         out = attention_ops.attend_biased(ctx, ctx.plan(self), qkv, kv, nq, nkv, dk, dv, self.window, 0, self.scale, None, None,
-                                          self.sink)
+                                          self.sink, softcap=self.softcap)
         return self.o_proj(out, residual=residual)
 
 

@@ -31,6 +31,18 @@ class TensorSpec:
     init: str = "matrix"            # "matrix": N(0, std); "norm": 1 + N(0, std); "bias": N(0, std)
     optional: bool = False          # may be absent from a checkpoint (e.g. a tied head)
 
+    # A size of -1 is one that the checkpoint decides (the part reads it off the tensor when it loads);
+    # random weights take FREE_SIZE there.
+    def fits(self, shape) -> bool:
+        shape = tuple(int(d) for d in shape)
+        return len(shape) == len(self.shape) and all(w in (-1, d) for w, d in zip(self.shape, shape))
+
+    def drawn_shape(self) -> Tuple[int, ...]:
+        return tuple(FREE_SIZE if d == -1 else d for d in self.shape)
+
+
+FREE_SIZE = 16
+
 
 @dataclass(frozen=True)
 class KVCacheNeed:
@@ -104,6 +116,11 @@ class Part:
 
     def plan_step(self, host) -> Dict[str, object]:
         return {}
+
+    # Parts that this part is made of and runs itself (mixers side by side): they are asked for their work lists
+    # like parts of the model's own, and counted with it.
+    def sub_parts(self) -> Sequence["Part"]:
+        return ()
 
 
 class Norm(Part):
@@ -228,6 +245,7 @@ POSITION_ENCODINGS: Dict[str, type] = {}
 BLOCKS: Dict[str, type] = {}
 EMBEDDINGS: Dict[str, type] = {}
 HEADS: Dict[str, type] = {}
+STREAM_PARTS: Dict[str, type] = {}      # what is done to the residual stream between layers (``parts/stream.py``)
 
 
 def _register(table: Dict[str, type], kind: str):
@@ -247,6 +265,7 @@ def register_position_encoding(kind): return _register(POSITION_ENCODINGS, kind)
 def register_block(kind): return _register(BLOCKS, kind)
 def register_embedding(kind): return _register(EMBEDDINGS, kind)
 def register_head(kind): return _register(HEADS, kind)
+def register_stream_part(kind): return _register(STREAM_PARTS, kind)
 
 
 def build_part(table: Dict[str, type], spec, what: str, **extra):

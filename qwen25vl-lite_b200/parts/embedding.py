@@ -16,9 +16,11 @@ from .base import Part, TensorSpec, register_embedding, register_head
 class TokenEmbedding(Part):
     graph_safe = True                # forward is a fixed sequence of this engine's kernels
 
-    def __init__(self, vocab_size: int, hidden_size: int, name: str = "weight"):
-        """``name``: what the table is called in a checkpoint, after the part's prefix."""
+    def __init__(self, vocab_size: int, hidden_size: int, name: str = "weight", scale: float = 1.0):
+        """``name``: what the table is called in a checkpoint, after the part's prefix.  ``scale``: the rows are
+        multiplied by it on their way into the residual stream (the table itself, which a tied head reads, is not)."""
         self.vocab_size, self.hidden_size, self.name = int(vocab_size), int(hidden_size), name
+        self.scale = float(scale)
         self.weight = None
 
     def tensor_specs(self):
@@ -32,7 +34,7 @@ class TokenEmbedding(Part):
 
     def forward(self, ctx):
         x = torch.empty((ctx.n_tokens, self.hidden_size), dtype=torch.float32, device=self.weight.device)
-        kernels.embed_gather(self.weight, ctx.token_ids, x)
+        kernels.embed_gather(self.weight, ctx.token_ids, x, self.scale)
         return x
 
 

@@ -1,4 +1,4 @@
-"""RMS normalisation fused with the residual update.
+"""Normalisations fused with the residual update: RMS norm, Dynamic Tanh, layer norm.
 
 Formula (reference src/qwen25vl_lite/layers.py:27-31): ``x * rsqrt(mean(x^2) + eps) * w``,
 statistics in float32, plain (not 1 + w) weight.  With ``groups`` > 1 the vector is cut into
@@ -100,3 +100,57 @@ class DynamicTanh(Norm):
         out = torch.empty((n_out, self.dim), dtype=ctx.dtype, device=x.device)
         kernels.add_dyt(x, delta, self.weight, self.bias, self.alpha, out, rows)
         return out
+
+
+@register_norm("layernorm")
+class LayerNorm(Norm):
+    """Layer norm with weight and bias: ``(x - mean) / sqrt(var + eps) * w + b``, var the mean of the squared
+    deviations, statistics in float32.  The bias stands beside the weight in a checkpoint as ``<name>.b``.
+
+    ``scale_name``: a learned vector (its full checkpoint name, e.g. a layer scale) that multiplies the norm's
+    result channel by channel; it is folded into weight and bias when the part is loaded, so it costs nothing
+    at run time.  As the norm of a pending update (``x += norm(update)``) it runs inside the kernel that adds
+    the update and normalises for the next sublayer."""
+
+    graph_safe = True                # forward is a fixed sequence of this engine's kernels
+
+    def __init__(self, dim: int, eps: float, name: str = "weight", optional: bool = False, scale_name: str = None):
+        self.dim, self.eps, self.name, self.optional = int(dim), float(eps), name, bool(optional)
+        self.scale_name = scale_name
+        self.weight = self.bias = None
+
+    def tensor_specs(self):
+        o = self.optional
+        specs = [TensorSpec(self.name, (self.dim,), init="norm", optional=o), TensorSpec(self.name + ".b", (self.dim,), init="bias", optional=o)]
+        if self.scale_name:
+            specs.append(TensorSpec(self.scale_name, (self.dim,), init="fraction", optional=o))
+        return tuple(specs)
+
+    def load(self, tensors, device, dtype):
+        names = [self.name, self.name + ".b"] + ([self.scale_name] if self.scale_name else [])
+        if not all(n in tensors for n in names):
+            if self.optional:
+                return
+            raise KeyError(next(n for n in names if n not in tensors))
+        w = tensors[self.name].to(device=device, dtype=torch.float32)
+        b = tensors[self.name + ".b"].to(device=device, dtype=torch.float32)
+        if self.scale_name:
+            s = tensors[self.scale_name].to(device=device, dtype=torch.float32)
+            w, b = w * s, b * s
+        self.weight, self.bias = w.contiguous(), b.contiguous()
+
+    def forward(self, ctx, x, delta, rows=None, defer=False):
+        post = None
+        if isinstance(delta, PendingUpdate):
+            post, delta = delta.norm, delta.value
+            if not isinstance(post, LayerNorm):
+                raise TypeError("a pending update on its way into a layernorm can be normalised by a layernorm only")
+        n_out = x.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((n_out, self.dim), dtype=ctx.dtype, device=x.device)
+        kernels.add_layernorm(x, delta, None if post is None else post.weight, None if post is None else post.bias, None,
+                              0.0 if post is None else post.eps, self.weight, self.bias, self.eps, out, rows)
+        return out
+
+    def add_only(self, ctx, x, value):
+        """x += norm(value) with this norm, and nothing else: for a pending update that no norm follows."""
+        kernels.add_layernorm(x, value, self.weight, self.bias, None, self.eps, None, None, 0.0, None, None, dtype=ctx.dtype)

@@ -76,7 +76,7 @@ def load_model(model_dir: str, dtype: str = "float32", device: str = "cuda:0"):
     missing = [n for n, ts in expected.items() if n not in where and not ts.optional]
     wrong = []
     for name, (f, raw_name) in where.items():
-        if tuple(f.shape(raw_name)) != tuple(expected[name].shape):
+        if not expected[name].fits(f.shape(raw_name)):
             wrong.append(f"{raw_name}: file has {list(f.shape(raw_name))}, model needs {list(expected[name].shape)}")
         elif not f.dtype(raw_name).is_floating_point:
             wrong.append(f"{raw_name}: file stores {f.dtype(raw_name)}, model needs a floating-point tensor")

@@ -28,9 +28,9 @@ def _draw(ts, gen: torch.Generator, device) -> torch.Tensor:
     small matrices whose products should not all be near zero (routers, gates of a recurrence);
     ``positive``: uniform in [0.05, 1); ``fraction``: uniform in [0.2, 0.8)."""
     if ts.init in ("positive", "fraction"):
-        t = torch.rand(ts.shape, generator=gen, dtype=torch.float32, device=device)
+        t = torch.rand(ts.drawn_shape(), generator=gen, dtype=torch.float32, device=device)
         return t * 0.95 + 0.05 if ts.init == "positive" else t * 0.6 + 0.2
-    t = torch.randn(ts.shape, generator=gen, dtype=torch.float32, device=device) * STD
+    t = torch.randn(ts.drawn_shape(), generator=gen, dtype=torch.float32, device=device) * STD
     if ts.init == "norm":
         t += 1.0
     elif ts.init == "matrix_wide":
