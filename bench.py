@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the engine at Qwen2.5-VL sizes, random bfloat16 weights.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 3b|7b-trace|32b|rirulix|labolix]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 3b|7b-trace|32b|rirulix|labolix|mozutar]
 
 One "step" is one decode step of the whole batch.  The default run (``--config 3b``) has the 3B
 layer sizes: the headline ``value`` is decoded tokens a second at batch 8 after 2,048-token
@@ -11,7 +11,7 @@ out every step).  The same line carries the 2,048-token prefill, the decode step
 decode at batch 1 and 64, the clocks seen while timing, and the number of this engine's kernel
 launches in the timed region.  ``--config 7b-trace`` runs a continuous-batching trace of 128
 requests at the 7B sizes, ``--config 32b`` decode at batch 1 / 8 / 32 after 8,192-token prompts and
-a 2,048-token prefill at the 32B sizes, ``--config rirulix`` / ``--config labolix`` prefill and decode of the Rirulix / Labolix design
+a 2,048-token prefill at the 32B sizes, ``--config rirulix`` / ``--config labolix`` / ``--config mozutar`` prefill and decode of the Rirulix / Labolix / Mozutar design
 at a few layer sizes beside this decoder at equal size; each prints one line of its own.
 The engine is single-GPU: for --gpus N > 1 one line says so and the exit code is 2.
 """
@@ -509,6 +509,32 @@ LABOLIX_SIZES = {
 }
 
 
+def _mozutar_sizes(width, layers, heads, kv_heads, dim, mem_heads, mem_dim, rank, experts, identity, groups, keep, top, ff, dense_ff, vocab):
+    """A Mozutar model of ``layers`` layers (softmax beside gated linear attention with a dense feed-forward, the same
+    with routed experts, an mLSTM with routed experts, and so on; the middle layers form a stretch that is entered
+    through the product over the stream and the embedding) and the Qwen2.5-VL text decoder of equal size beside
+    it: the same width, layers, heads and vocabulary, a feed-forward as wide as the dense one."""
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "identity": identity, "top": top, "groups": {"count": groups, "keep": keep}}}
+    dense = {"kind": "dense", "ff": dense_ff}
+    par = {"type": "parallel", "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0,
+                                                  "rot": {"dims": dim // 2, "base": 10000.0}},
+                                         "right": {"heads": mem_heads, "dim": mem_dim, "vdim": mem_dim, "tau": 16.0, "rank": rank}}}
+    mem = {"type": "mlstm", "mixer": {"heads": mem_heads, "dim": mem_dim, "vdim": mem_dim, "gate_cap": 15.0}}
+    ours = {"architecture": "Mozutar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
+            "loop": {"start": 1, "stop": layers - 1, "times": 1},
+            "layers": [dict((par, par, mem)[i % 3], mlp=(dense, moe, moe)[i % 3]) for i in range(layers)]}
+    closest = _sizes(width, layers, heads, kv_heads, dense_ff, vocab, True)
+    closest["text_config"]["rope_scaling"]["mrope_section"] = [dim // 8, 3 * dim // 16, 3 * dim // 16]
+    return ours, closest
+
+
+MOZUTAR_SIZES = {
+    "w1024": _mozutar_sizes(1024, 6, 8, 2, 128, 8, 128, 16, 6, 2, 4, 2, 2, 1408, 2816, 32000),
+    "w2048": _mozutar_sizes(2048, 6, 16, 2, 128, 16, 128, 32, 14, 2, 4, 2, 2, 2816, 5632, 32000),
+    "w2560_d64": _mozutar_sizes(2560, 6, 40, 8, 64, 40, 64, 32, 28, 4, 8, 4, 4, 1728, 6912, 32000),
+}
+
+
 def run_rirulix(args):
     """Prefill and decode throughput of the Rirulix design at a few layer sizes, each beside the
     Qwen2.5-VL text decoder of equal size, random weights: a 2,048-token prompt in one step, and
@@ -520,6 +546,11 @@ def run_labolix(args):
     """The same measurement for the Labolix design: a 2,048-token prompt in one step, decode steps at
     batch 8 and 64 after 1,024-token prompts, each size beside the Qwen2.5-VL text decoder of equal size."""
     return _run_design(args, "Labolix", "labolix", LABOLIX_SIZES)
+
+
+def run_mozutar(args):
+    """The same measurement for the Mozutar design."""
+    return _run_design(args, "Mozutar", "mozutar", MOZUTAR_SIZES)
 
 
 def _run_design(args, design, label_ours, all_sizes):
@@ -578,9 +609,9 @@ def main(argv=None):
     ap.add_argument("--only-batch", type=int, default=0, help="time decode steps at this batch size only (for profilers)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
                     help="float32 times the true 32-bit path of the 3b configuration (fewer --layers advised)")
-    ap.add_argument("--only-size", default="", help="with --config rirulix or labolix: one of its sizes only (for profilers)")
-    ap.add_argument("--config", default="3b", choices=["3b", "7b-trace", "32b", "rirulix", "labolix"],
-                    help="3b: the headline line (default); 7b-trace, 32b: the other workloads, one line each; rirulix, labolix: "
+    ap.add_argument("--only-size", default="", help="with --config rirulix, labolix or mozutar: one of its sizes only (for profilers)")
+    ap.add_argument("--config", default="3b", choices=["3b", "7b-trace", "32b", "rirulix", "labolix", "mozutar"],
+                    help="3b: the headline line (default); 7b-trace, 32b: the other workloads, one line each; rirulix, labolix, mozutar: "
                          "that design at a few layer sizes beside the Qwen2.5-VL decoder of equal size")
     args = ap.parse_args(argv)
     if args.gpus != 1:
@@ -593,7 +624,7 @@ def main(argv=None):
             print(json.dumps({"impl": "reference", "unavailable": "the reference arm measures the 3b configuration only"}))
             return 0
         return run_reference(args)
-    return {"3b": run_ours, "7b-trace": run_7b_trace, "32b": run_32b, "rirulix": run_rirulix, "labolix": run_labolix}[args.config](args)
+    return {"3b": run_ours, "7b-trace": run_7b_trace, "32b": run_32b, "rirulix": run_rirulix, "labolix": run_labolix, "mozutar": run_mozutar}[args.config](args)
 
 
 if __name__ == "__main__":

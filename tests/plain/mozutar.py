@@ -75,13 +75,14 @@ def capped_attention(h, t, m, eps):
     rot = m.get("rot") or {"dims": 0, "base": 1.0}
     q = rotate_halves(q, int(rot["dims"]), float(rot["base"]), pos)
     k = rotate_halves(k, int(rot["dims"]), float(rot["base"]), pos)
-    cap = float(m["softcap"])
+    cap = float(m.get("softcap") or 0.0)              # absent or 0: the scores stay as they are
     out = np.zeros((T, H, v.shape[-1]))
     visible = np.tril(np.ones((T, T), dtype=bool))
     for head in range(H):
         g = head // (H // G)
         s = (q[:, head] @ k[:, g].T) * float(m["scale"])
-        s = cap * np.tanh(s / cap)
+        if cap:
+            s = cap * np.tanh(s / cap)
         s = np.where(visible, s, -np.inf)
         s = s - s.max(axis=-1, keepdims=True)
         p = np.exp(s)
@@ -172,7 +173,7 @@ def route(h, router, correction, r):
 def routed_ffn(h, t, mlp):
     r = mlp["router"]
     real = int(r["experts"])                      # router outputs beyond these are experts that return their input
-    chosen, weights = route(h, t["router"], t["correction"], r)
+    chosen, weights = route(h, t["router"], t.get("correction", 0.0), r)
     out = np.zeros_like(h)
     for i in range(h.shape[0]):
         for e, w in zip(chosen[i], weights[i]):
@@ -210,7 +211,7 @@ def forward(config, tensors, tokens, layers_out=None):
     w = {k: np.asarray(v, dtype=np.float64) for k, v in tensors.items()}
     eps = float(config["norm"]["eps"])
     tokens = np.asarray(tokens)
-    x = w["embed"][tokens] * float(config["embedding"]["scale"])
+    x = w["embed"][tokens] * float((config.get("embedding") or {}).get("scale", 1.0))
     x0 = x.copy()
     for i, begins in layer_order(config):
         if begins is not None:
@@ -234,3 +235,35 @@ def forward(config, tensors, tokens, layers_out=None):
             layers_out.append(x.copy())
     x = layer_norm(x, w["final.norm"], w["final.norm.b"], eps)
     return x @ w["embed"].T
+
+
+# ---- model folders, generation ---------------------------------------------------------------------
+
+def load_model_dir(folder, dtype=np.float64):
+    """(raw config.json dictionary, tensors by name) of a model folder."""
+    import json
+    import os
+
+    from .decoder import read_safetensors
+
+    with open(os.path.join(folder, "config.json"), encoding="utf-8") as fh:
+        config = json.load(fh)
+    return config, {k: np.asarray(v, dtype=dtype) for k, v in read_safetensors(os.path.join(folder, "model.safetensors")).items()}
+
+
+def forward_logits(config, w, tokens):
+    return forward(config, w, tokens)
+
+
+def greedy_generate(config, w, prompt, n):
+    ids = list(prompt)
+    for _ in range(n):
+        ids.append(int(np.argmax(forward(config, w, ids)[-1])))
+    return ids[len(prompt):]
+
+
+def generation_margins(config, w, prompt, generated):
+    """For every generated token: how far its plain logit lies below the largest one at its place."""
+    logits = forward(config, w, list(prompt) + list(generated))
+    at = len(prompt) - 1
+    return [float(logits[at + i].max() - logits[at + i, t]) for i, t in enumerate(generated)]
