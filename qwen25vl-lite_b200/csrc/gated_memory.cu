@@ -17,6 +17,17 @@
 // slices are added in slice order and o_t goes to memory as floats.  The order of every sum depends on the sizes
 // alone, so a token's result does not depend on where its run was cut or on the batch.
 //
+// Long runs are cut into chunks of tokens that are walked in parallel (the host plans them; `items` then says what
+// every CTA row of the grid walks).  Pass 1 walks every chunk from an empty memory (S = 0, m = -inf), without outputs,
+// and leaves in scratch the chunk's own sum L, with what the fold needs to carry a state across the chunk: the
+// product of the chunk's decays per key channel, or the sum of its log forget gates and its own maximum.
+// memory_fold_kernel then goes over a run's chunks in order, an element of S per thread: it leaves every chunk the
+// state before it (in place of L) and the request the state after the last one: S <- A S + L per channel, or
+// m' = max(F + m, m_L), S <- exp(F + m - m') S + exp(m_L - m') L per head.  Pass 2 walks every chunk again, from the
+// state before it, with outputs; runs too short to cut are walked in pass 2 from and to the request's state.  A
+// chunk's border moves rounding only: the fold multiplies by the product of the decays where the walk multiplies
+// token by token.
+//
 // The output (memory_output_kernel, a warp per token and head): o_t divided by max(|n_t . q_t|, exp(-m_t)) + 1e-6
 // where the memory has a normaliser; divided by its root mean square over the head's Dv channels (eps inside the
 // root); times a weight per channel; times silu or sigmoid of the token's gate channel; in T.
@@ -91,7 +102,14 @@ struct MemoryArgs {
   float* o_raw;             // [N, H, Dv + extra]
   float* m_exp;             // [N, H]: exp(-m_t) (gates per head)
   int H, D, Dv, extra;
+  // with items: CTA row y walks items[y] = (first token row, end, source, destination, flags) instead of entry y
+  const int* items;
+  float* scratch;           // [chunks][H][D + extra][Dv + extra]: states between chunks
+  float* aux;               // per channel [chunks][H][D]: the product of a chunk's decays; per head [chunks][H][2]: sum of log f, the chunk's own m
 };
+
+#define GM_SRC_SCRATCH 1    // the walk starts from scratch[source] (else from the state of entry `source`)
+#define GM_DST_NONE 2       // the state after the walk is not kept (else it goes back to where it came from)
 
 // (a, b) stands for x -> max(x + a, b); `first` then `second` is x -> max(x + a1 + a2, max(b1 + a2, b2)).
 __device__ __forceinline__ void maxplus_after(float& a, float& b, float a1, float b1) {
@@ -99,7 +117,8 @@ __device__ __forceinline__ void maxplus_after(float& a, float& b, float a1, floa
   a = a1 + a;
 }
 
-template <typename T, int RPT, bool PER_HEAD>
+// LOCAL: pass 1 of a cut run (from an empty memory, no outputs, the chunk's sum and its carry factors to scratch).
+template <typename T, int RPT, bool PER_HEAD, bool LOCAL>
 __global__ void memory_scan_kernel(MemoryArgs p) {
   pdl_trigger();
   pdl_wait();
@@ -114,17 +133,33 @@ __global__ void memory_scan_kernel(MemoryArgs p) {
   float* a_s = k_s + GM_TOKENS * Dp;                     // per channel: [GM_TOKENS][Dp]; per head: [GM_TOKENS] a_t, [GM_TOKENS] b_t, m
   float* v_s = a_s + (PER_HEAD ? 2 * GM_TOKENS + 4 : GM_TOKENS * Dp);      // [GM_TOKENS][GM_COLS]
   float* part = v_s + GM_TOKENS * GM_COLS;               // [GM_TOKENS][DG][GM_COLS]
-  const int begin = p.cu_q[seq], end = p.cu_q[seq + 1];
-  float* st = p.state + ((size_t)p.slot_ids[seq] * p.H + head) * (size_t)(p.D + p.extra) * cols;
+  const size_t st_floats = (size_t)(p.D + p.extra) * cols;
+  int begin, end, flags = 0;
+  float* st;
+  if (p.items) {
+    const int* it = p.items + 5 * seq;
+    begin = it[0]; end = it[1]; flags = it[4];
+    if (LOCAL) st = p.scratch + ((size_t)it[3] * p.H + head) * st_floats;
+    else if (flags & GM_SRC_SCRATCH) st = p.scratch + ((size_t)it[2] * p.H + head) * st_floats;
+    else st = p.state + ((size_t)p.slot_ids[it[2]] * p.H + head) * st_floats;
+  } else {
+    begin = p.cu_q[seq]; end = p.cu_q[seq + 1];
+    st = p.state + ((size_t)p.slot_ids[seq] * p.H + head) * st_floats;
+  }
+  const int chunk = p.items ? p.items[5 * seq + 3] : 0;
   const T* x = (const T*)p.x;
 
   float S[RPT];
+  float P[LOCAL && !PER_HEAD ? RPT : 1];                 // pass 1, decays per channel: their product over the chunk
 #pragma unroll
   for (int i = 0; i < RPT; ++i) {
     const int r = g * RPT + i;
-    S[i] = (r < p.D && col_ok) ? st[(size_t)r * cols + col] : 0.f;
+    S[i] = (!LOCAL && r < p.D && col_ok) ? st[(size_t)r * cols + col] : 0.f;
+    if (LOCAL && !PER_HEAD) P[i] = 1.f;
   }
-  float m_carry = PER_HEAD ? st[(size_t)p.D * cols + col0] : 0.f;     // every column keeps a copy of m; the CTA reads its first
+  // every column keeps a copy of m; the CTA reads its first
+  float m_carry = PER_HEAD ? (LOCAL ? -INFINITY : st[(size_t)p.D * cols + col0]) : 0.f;
+  float f_sum = 0.f;                                     // pass 1, gates per head: the sum of the chunk's log forget gates
 
   for (int t0 = begin; t0 < end; t0 += GM_TOKENS) {
     const int nt = min(GM_TOKENS, end - t0);
@@ -133,7 +168,7 @@ __global__ void memory_scan_kernel(MemoryArgs p) {
       const int t = i / Dp, r = i % Dp;
       const size_t row = (size_t)(t0 + t) * p.x_stride;
       const bool ok = r < p.D;
-      q_s[i] = ok ? to_f32(x[row + p.q_off + head * p.D + r]) * p.q_scale : 0.f;
+      if (!LOCAL) q_s[i] = ok ? to_f32(x[row + p.q_off + head * p.D + r]) * p.q_scale : 0.f;
       k_s[i] = ok ? to_f32(x[row + p.k_off + head * p.D + r]) : 0.f;
       if (!PER_HEAD) a_s[i] = ok ? p.decay[((size_t)(t0 + t) * p.H + head) * p.D + r] : 0.f;
     }
@@ -164,12 +199,12 @@ __global__ void memory_scan_kernel(MemoryArgs p) {
       if (lane < nt) {
         a_s[lane] = expf(lf + m_prev - m_t);
         a_s[GM_TOKENS + lane] = expf(li - m_t);
-        if (blockIdx.z == 0) p.m_exp[(size_t)(t0 + lane) * p.H + head] = expf(-m_t);
+        if (!LOCAL && blockIdx.z == 0) p.m_exp[(size_t)(t0 + lane) * p.H + head] = expf(-m_t);
       }
-      if (lane == nt - 1) a_s[2 * GM_TOKENS] = m_t;
+      if (lane == nt - 1) { a_s[2 * GM_TOKENS] = m_t; a_s[2 * GM_TOKENS + 1] = a; }       // a: the sum of the batch's log f
     }
     __syncthreads();
-    if (PER_HEAD) m_carry = a_s[2 * GM_TOKENS];
+    if (PER_HEAD) { m_carry = a_s[2 * GM_TOKENS]; f_sum += a_s[2 * GM_TOKENS + 1]; }
     for (int t = 0; t < nt; ++t) {
       const float4* q4 = reinterpret_cast<const float4*>(q_s + t * Dp + g * RPT);
       const float4* k4 = reinterpret_cast<const float4*>(k_s + t * Dp + g * RPT);
@@ -179,19 +214,26 @@ __global__ void memory_scan_kernel(MemoryArgs p) {
       float acc = 0.f;
 #pragma unroll
       for (int i = 0; i < RPT / 4; ++i) {
-        const float4 qq = q4[i], kk = k4[i];
-        float4 aa;
+        const float4 kk = k4[i];
+        float4 qq = make_float4(0.f, 0.f, 0.f, 0.f), aa;
+        if (!LOCAL) qq = q4[i];
         if (PER_HEAD) aa = make_float4(a_head, a_head, a_head, a_head);
         else aa = a4[i];
-        S[4 * i + 0] = fmaf(aa.x, S[4 * i + 0], kk.x * v); acc = fmaf(S[4 * i + 0], qq.x, acc);
-        S[4 * i + 1] = fmaf(aa.y, S[4 * i + 1], kk.y * v); acc = fmaf(S[4 * i + 1], qq.y, acc);
-        S[4 * i + 2] = fmaf(aa.z, S[4 * i + 2], kk.z * v); acc = fmaf(S[4 * i + 2], qq.z, acc);
-        S[4 * i + 3] = fmaf(aa.w, S[4 * i + 3], kk.w * v); acc = fmaf(S[4 * i + 3], qq.w, acc);
+        S[4 * i + 0] = fmaf(aa.x, S[4 * i + 0], kk.x * v);
+        S[4 * i + 1] = fmaf(aa.y, S[4 * i + 1], kk.y * v);
+        S[4 * i + 2] = fmaf(aa.z, S[4 * i + 2], kk.z * v);
+        S[4 * i + 3] = fmaf(aa.w, S[4 * i + 3], kk.w * v);
+        if (LOCAL) {
+          if (!PER_HEAD) { P[4 * i + 0] *= aa.x; P[4 * i + 1] *= aa.y; P[4 * i + 2] *= aa.z; P[4 * i + 3] *= aa.w; }
+        } else {
+          acc = fmaf(S[4 * i + 0], qq.x, acc); acc = fmaf(S[4 * i + 1], qq.y, acc);
+          acc = fmaf(S[4 * i + 2], qq.z, acc); acc = fmaf(S[4 * i + 3], qq.w, acc);
+        }
       }
-      part[(t * DG + g) * GM_COLS + lane] = acc;
+      if (!LOCAL) part[(t * DG + g) * GM_COLS + lane] = acc;
     }
     __syncthreads();
-    if (col_ok) {
+    if (!LOCAL && col_ok) {
       for (int t = g; t < nt; t += DG) {
         float o = 0.f;
         for (int s = 0; s < DG; ++s) o += part[(t * DG + s) * GM_COLS + lane];
@@ -199,6 +241,7 @@ __global__ void memory_scan_kernel(MemoryArgs p) {
       }
     }
   }
+  if (!LOCAL && (flags & GM_DST_NONE)) return;
   if (col_ok) {
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
@@ -207,6 +250,55 @@ __global__ void memory_scan_kernel(MemoryArgs p) {
     }
     if (PER_HEAD && g == 0) st[(size_t)p.D * cols + col] = m_carry;
   }
+  if (LOCAL && blockIdx.z == 0 && lane == 0) {
+    if (PER_HEAD) {
+      if (g == 0) { p.aux[((size_t)chunk * p.H + head) * 2] = f_sum; p.aux[((size_t)chunk * p.H + head) * 2 + 1] = m_carry; }
+    } else {
+#pragma unroll
+      for (int i = 0; i < RPT; ++i) {
+        const int r = g * RPT + i;
+        if (r < p.D) p.aux[((size_t)chunk * p.H + head) * p.D + r] = P[LOCAL && !PER_HEAD ? i : 0];
+      }
+    }
+  }
+}
+
+// A run's chunks in order, an element of the state per thread.  runs[y] = (entry, first chunk, chunks).
+template <bool PER_HEAD>
+__global__ void __launch_bounds__(256) memory_fold_kernel(MemoryArgs p, const int* __restrict__ runs) {
+  pdl_trigger();
+  pdl_wait();
+  const int head = blockIdx.x, cols = p.Dv + p.extra;
+  const int* run = runs + 3 * blockIdx.y;
+  const int first = run[1], n_chunks = run[2];
+  const size_t st_floats = (size_t)(p.D + p.extra) * cols;
+  const size_t e = (size_t)blockIdx.z * 256 + threadIdx.x;
+  if (e >= st_floats) return;
+  const int r = (int)(e / cols);
+  float* st = p.state + ((size_t)p.slot_ids[run[0]] * p.H + head) * st_floats;
+  float s = st[e];                                        // row D (per head): m, a copy in every column
+  float m = PER_HEAD ? st[(size_t)p.D * cols] : 0.f;
+  for (int c = 0; c < n_chunks; ++c) {
+    float* sc = p.scratch + ((size_t)(first + c) * p.H + head) * st_floats;
+    const float local = sc[e];
+    if (PER_HEAD) {
+      const float* ax = p.aux + ((size_t)(first + c) * p.H + head) * 2;
+      const float f = ax[0], m_local = ax[1];
+      const float m_new = fmaxf(f + m, m_local);
+      if (r == p.D) {
+        sc[e] = m;
+        s = m_new;
+      } else {
+        sc[e] = s;
+        s = fmaf(expf(f + m - m_new), s, expf(m_local - m_new) * local);
+      }
+      m = m_new;
+    } else {
+      sc[e] = s;
+      s = fmaf(p.aux[((size_t)(first + c) * p.H + head) * p.D + r], s, local);
+    }
+  }
+  st[e] = s;
 }
 
 // A warp per (token, head).  act: 0 = silu of the gate channel, 1 = sigmoid.
@@ -279,8 +371,8 @@ Q25_EXPORT int q25_memory_row_dots_bf16(const void* h, const float* w, const flo
   return row_dots<bf16>(h, w, b, out, n, hidden, rows, s);
 }
 
-template <typename T, int RPT, bool PER_HEAD>
-static int memory_scan_shape(const MemoryArgs& p, int n_seqs, cudaStream_t s) {
+template <typename T, int RPT, bool PER_HEAD, bool LOCAL>
+static int memory_scan_shape(const MemoryArgs& p, int n_rows, cudaStream_t s) {
   const int DG = (p.D + RPT - 1) / RPT, Dp = DG * RPT;
   const int cols = p.Dv + p.extra;
   const size_t floats = (size_t)2 * GM_TOKENS * Dp + (PER_HEAD ? 2 * GM_TOKENS + 4 : GM_TOKENS * Dp) + GM_TOKENS * GM_COLS +
@@ -288,11 +380,24 @@ static int memory_scan_shape(const MemoryArgs& p, int n_seqs, cudaStream_t s) {
   const size_t smem = floats * sizeof(float);
   if (smem > 200 * 1024 || DG > 16) return (int)cudaErrorInvalidValue;
   if (smem > 48 * 1024) {
-    const cudaError_t e = cudaFuncSetAttribute(memory_scan_kernel<T, RPT, PER_HEAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const cudaError_t e = cudaFuncSetAttribute(memory_scan_kernel<T, RPT, PER_HEAD, LOCAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  launch(memory_scan_kernel<T, RPT, PER_HEAD>, dim3(p.H, n_seqs, (cols + GM_COLS - 1) / GM_COLS), dim3(GM_COLS, DG), smem, s, p);
+  launch(memory_scan_kernel<T, RPT, PER_HEAD, LOCAL>, dim3(p.H, n_rows, (cols + GM_COLS - 1) / GM_COLS), dim3(GM_COLS, DG), smem, s, p);
   return launch_status();
+}
+
+template <typename T, bool LOCAL>
+static int memory_scan_rows(const MemoryArgs& p, int n_rows, cudaStream_t s) {
+  if (n_rows <= 0) return 0;
+  if (p.extra) {
+    if (p.D <= 64) return memory_scan_shape<T, 16, true, LOCAL>(p, n_rows, s);
+    if (p.D <= 128) return memory_scan_shape<T, 32, true, LOCAL>(p, n_rows, s);
+    return memory_scan_shape<T, 64, true, LOCAL>(p, n_rows, s);
+  }
+  if (p.D <= 64) return memory_scan_shape<T, 16, false, LOCAL>(p, n_rows, s);
+  if (p.D <= 128) return memory_scan_shape<T, 32, false, LOCAL>(p, n_rows, s);
+  return memory_scan_shape<T, 64, false, LOCAL>(p, n_rows, s);
 }
 
 // per_head 0: decays per key channel from `decay`; 1: gates per head from `gates`, with a normaliser column and m in the state.
@@ -306,15 +411,51 @@ static int memory_scan(const void* x, int x_stride, int q_off, int k_off, int v_
   p.x = x; p.x_stride = x_stride; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off; p.decay = decay; p.gates = gates; p.cap = cap;
   p.q_scale = q_scale; p.state = state; p.cu_q = cu_q; p.slot_ids = slot_ids; p.o_raw = o_raw; p.m_exp = m_exp;
   p.H = H; p.D = D; p.Dv = Dv; p.extra = per_head ? 1 : 0;
+  p.items = nullptr; p.scratch = nullptr; p.aux = nullptr;
+  return memory_scan_rows<T, false>(p, n_seqs, (cudaStream_t)stream);
+}
+
+// A step with long runs cut into chunks.  first [n_first, 5]: the chunks of pass 1 (token rows, -, chunk, -); runs
+// [n_runs, 3]: (entry, first chunk, chunks); second [n_second, 5]: what pass 2 walks, the chunks (from scratch, state not
+// kept) and the entries that were not cut (from and to their state).
+template <typename T>
+static int memory_scan_chunked(const void* x, int x_stride, int q_off, int k_off, int v_off, const float* decay, const float* gates, float cap,
+                               float q_scale, float* state, const int* slot_ids, float* o_raw, float* m_exp, const int* first, int n_first,
+                               const int* runs, int n_runs, const int* second, int n_second, float* scratch, float* aux, int H, int D, int Dv,
+                               int per_head, void* stream) {
+  if (H <= 0 || D <= 0 || Dv <= 0 || D > 512 || (per_head ? (!gates || !m_exp) : !decay) || !scratch || !aux) return (int)cudaErrorInvalidValue;
+  MemoryArgs p;
+  p.x = x; p.x_stride = x_stride; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off; p.decay = decay; p.gates = gates; p.cap = cap;
+  p.q_scale = q_scale; p.state = state; p.cu_q = nullptr; p.slot_ids = slot_ids; p.o_raw = o_raw; p.m_exp = m_exp;
+  p.H = H; p.D = D; p.Dv = Dv; p.extra = per_head ? 1 : 0; p.scratch = scratch; p.aux = aux;
   cudaStream_t s = (cudaStream_t)stream;
-  if (per_head) {
-    if (D <= 64) return memory_scan_shape<T, 16, true>(p, n_seqs, s);
-    if (D <= 128) return memory_scan_shape<T, 32, true>(p, n_seqs, s);
-    return memory_scan_shape<T, 64, true>(p, n_seqs, s);
+  p.items = first;
+  int rc = memory_scan_rows<T, true>(p, n_first, s);
+  if (rc) return rc;
+  if (n_runs > 0) {
+    const size_t st_floats = (size_t)(D + p.extra) * (Dv + p.extra);
+    const dim3 grid(H, n_runs, (unsigned)((st_floats + 255) / 256));
+    if (per_head) launch(memory_fold_kernel<true>, grid, dim3(256), 0, s, p, runs);
+    else launch(memory_fold_kernel<false>, grid, dim3(256), 0, s, p, runs);
+    rc = launch_status();
+    if (rc) return rc;
   }
-  if (D <= 64) return memory_scan_shape<T, 16, false>(p, n_seqs, s);
-  if (D <= 128) return memory_scan_shape<T, 32, false>(p, n_seqs, s);
-  return memory_scan_shape<T, 64, false>(p, n_seqs, s);
+  p.items = second;
+  return memory_scan_rows<T, false>(p, n_second, s);
+}
+Q25_EXPORT int q25_memory_scan_chunked_f32(const void* x, int xs, int qo, int ko, int vo, const float* decay, const float* gates, float cap, float qsc,
+                                           float* state, const int* slots, float* o_raw, float* m_exp, const int* first, int n_first,
+                                           const int* runs, int n_runs, const int* second, int n_second, float* scratch, float* aux, int H, int D,
+                                           int Dv, int per_head, void* s) {
+  return memory_scan_chunked<float>(x, xs, qo, ko, vo, decay, gates, cap, qsc, state, slots, o_raw, m_exp, first, n_first, runs, n_runs, second,
+                                    n_second, scratch, aux, H, D, Dv, per_head, s);
+}
+Q25_EXPORT int q25_memory_scan_chunked_bf16(const void* x, int xs, int qo, int ko, int vo, const float* decay, const float* gates, float cap, float qsc,
+                                            float* state, const int* slots, float* o_raw, float* m_exp, const int* first, int n_first,
+                                            const int* runs, int n_runs, const int* second, int n_second, float* scratch, float* aux, int H, int D,
+                                            int Dv, int per_head, void* s) {
+  return memory_scan_chunked<bf16>(x, xs, qo, ko, vo, decay, gates, cap, qsc, state, slots, o_raw, m_exp, first, n_first, runs, n_runs, second,
+                                   n_second, scratch, aux, H, D, Dv, per_head, s);
 }
 Q25_EXPORT int q25_memory_scan_f32(const void* x, int xs, int qo, int ko, int vo, const float* decay, const float* gates, float cap, float qsc,
                                    float* state, const int* cu, const int* slots, float* o_raw, float* m_exp, int n_seqs, int H, int D, int Dv,

@@ -50,6 +50,7 @@ _SIGNATURES = {
     "q25_memory_gla_decay": [_P, _I, _I, _I, _P, _P, _F, _P, _I, _I, _P],
     "q25_memory_row_dots": [_P, _P, _P, _P, _I, _I, _I, _P],
     "q25_memory_scan": [_P, _I, _I, _I, _I, _P, _P, _F, _F, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "q25_memory_scan_chunked": [_P, _I, _I, _I, _I, _P, _P, _F, _F, _P, _P, _P, _P, _P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P],
     "q25_memory_output": [_P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _F, _I, _P],
 }
 _UNTYPED = {
@@ -1161,6 +1162,59 @@ def memory_scan(x: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: Opti
         x.data_ptr(), x.stride(0), int(q_off), int(k_off), int(v_off), _ptr(decay), _ptr(gates), float(cap), float(q_scale), state.data_ptr(),
         cu_q.data_ptr(), slot_ids.data_ptr(), o_raw.data_ptr(), _ptr(m_exp), int(n_seqs), heads, dim, vdim, int(per_head), _stream()),
         "memory_scan")
+
+
+MEMORY_CHUNK = 64          # tokens of a chunk of a cut run
+MEMORY_CUT = 128           # runs of at least this many tokens are cut
+MEMORY_FROM_SCRATCH, MEMORY_STATE_NOT_KEPT = 1, 2
+
+
+def plan_memory(q_lens, chunk: int = MEMORY_CHUNK, cut: int = MEMORY_CUT):
+    """The work lists of ``memory_scan_chunked`` for a step whose entries bring ``q_lens`` tokens: ``first`` (a row per
+    chunk of a cut run: first token row, end, 0, chunk, 0), ``runs`` (entry, first chunk, chunks) and ``second`` (the
+    chunks again, from scratch and without keeping the state, then the entries that are walked whole: first row, end,
+    entry, 0, 0).  All empty when no entry is long enough to cut."""
+    first, runs, second, whole, row = [], [], [], [], 0
+    for entry, n in enumerate(q_lens):
+        if n >= cut:
+            pieces = -(-n // chunk)
+            runs.append((entry, len(first), pieces))
+            for c in range(pieces):
+                begin, index = row + c * chunk, len(first)
+                end = min(begin + chunk, row + n)
+                first.append((begin, end, 0, index, 0))
+                second.append((begin, end, index, index, MEMORY_FROM_SCRATCH | MEMORY_STATE_NOT_KEPT))
+        elif n > 0:
+            whole.append((row, row + n, entry, 0, 0))
+        row += n
+    if not runs:
+        return [], [], []
+    return first, runs, second + whole
+
+
+def memory_scan_chunked(x: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: Optional[torch.Tensor], gates: Optional[torch.Tensor],
+                        cap: float, q_scale: float, state: torch.Tensor, slot_ids: torch.Tensor, o_raw: torch.Tensor,
+                        m_exp: Optional[torch.Tensor], first: torch.Tensor, runs: torch.Tensor, second: torch.Tensor, heads: int, dim: int,
+                        vdim: int) -> None:
+    """``memory_scan`` for a step with long runs, by the work lists of ``plan_memory`` (flat int32 tensors on the device):
+    every chunk's own sum from an empty memory, the sums folded onto the requests' states in order, then every chunk's
+    outputs from the state before it, all chunks of a pass in parallel.  Equal to the walk up to rounding."""
+    per_head = gates is not None
+    extra = 1 if per_head else 0
+    _dev(state, torch.float32, "memory_scan_chunked state"); _dev(o_raw, torch.float32, "memory_scan_chunked out")
+    for t in (first, runs, second):
+        _dev(t, torch.int32, "memory_scan_chunked work list")
+    if tuple(state.shape[1:]) != (heads, dim + extra, vdim + extra) or x.stride(1) != 1 or o_raw.numel() != x.shape[0] * heads * (vdim + extra):
+        raise KernelError(f"memory_scan_chunked: the state must be [slots, {heads}, {dim + extra}, {vdim + extra}]")
+    if per_head == (decay is not None):
+        raise KernelError("memory_scan_chunked: decays per channel or gates per head, one of the two")
+    n_first = first.numel() // 5
+    scratch = torch.empty((n_first, heads, dim + extra, vdim + extra), dtype=torch.float32, device=x.device)
+    aux = torch.empty((n_first, heads, 2 if per_head else dim), dtype=torch.float32, device=x.device)
+    _check(_typed("q25_memory_scan_chunked", x.dtype)(
+        x.data_ptr(), x.stride(0), int(q_off), int(k_off), int(v_off), _ptr(decay), _ptr(gates), float(cap), float(q_scale), state.data_ptr(),
+        slot_ids.data_ptr(), o_raw.data_ptr(), _ptr(m_exp), first.data_ptr(), n_first, runs.data_ptr(), runs.numel() // 3, second.data_ptr(),
+        second.numel() // 5, scratch.data_ptr(), aux.data_ptr(), heads, dim, vdim, int(per_head), _stream()), "memory_scan_chunked")
 
 
 MEMORY_GATES = {"silu": 0, "sigmoid": 1}

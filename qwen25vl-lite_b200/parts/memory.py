@@ -18,11 +18,14 @@ and request, a float32 state ``S`` [dim, value_dim] from token to token: ``S_t =
 
 Float32 in both dtypes: the decays and gates from their pre-activations on (the gate rows of ``mlstm`` and the second
 factor of the decay's projection are float32 products in a fixed order), S, n, m, o and the norms.  The state is zero
-at admission, so a run of tokens may be cut anywhere.  Kernels: ``csrc/gated_memory.cu``.
+at admission, so a run of tokens may be cut anywhere.  Single tokens and short runs are walked token by token; a
+long run is cut into chunks that are walked in parallel, twice, with a fold over the chunks' sums in between
+(``plan_step``).  Kernels: ``csrc/gated_memory.cu``.
 """
 
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..ops import kernels
@@ -43,6 +46,23 @@ class _MatrixMemory(Mixer):
 
     def _sizes(self):
         return self.hidden_size, self.num_heads * self.head_dim, self.num_heads * self.value_dim
+
+    def plan_key(self):
+        return ("matrix_memory",)             # the chunks of a step's long runs do not depend on a layer's sizes
+
+    def plan_step(self, host):
+        first, runs, second = kernels.plan_memory(host.q_lens)
+        return {name: np.asarray(a, dtype=np.int32).reshape(-1) for name, a in (("first", first), ("runs", runs), ("second", second))}
+
+    def _scan(self, ctx, x, decay, gates, cap, stop, o_raw, m_exp):
+        H, D, Dv = self.num_heads, self.head_dim, self.value_dim
+        plan = ctx.plan(self)
+        if plan.get("first") is None:
+            kernels.memory_scan(x, 0, H * D, 2 * H * D, decay, gates, cap, float(D) ** -0.5, stop.state, ctx.cu_q, ctx.slot_ids, o_raw, m_exp,
+                                ctx.n_seqs, H, D, Dv)
+        else:
+            kernels.memory_scan_chunked(x, 0, H * D, 2 * H * D, decay, gates, cap, float(D) ** -0.5, stop.state, ctx.slot_ids, o_raw, m_exp,
+                                        plan["first"], plan["runs"], plan["second"], H, D, Dv)
 
     def _common_specs(self):
         h, qk, v = self._sizes()
@@ -90,8 +110,7 @@ class GatedLinearAttention(_MatrixMemory):
         decay = torch.empty((n, H * D), dtype=torch.float32, device=x.device)
         kernels.gla_decay(x, 2 * H * D + 2 * H * Dv, self.decay_rank, self.a2t, self.a2_bias, self.tau, decay)
         o_raw = torch.empty((n, H, Dv), dtype=torch.float32, device=x.device)
-        kernels.memory_scan(x, 0, H * D, 2 * H * D, decay, None, 0.0, float(D) ** -0.5, stop.state, ctx.cu_q, ctx.slot_ids, o_raw, None,
-                            ctx.n_seqs, H, D, Dv)
+        self._scan(ctx, x, decay, None, 0.0, stop, o_raw, None)
         out = torch.empty((n, H * Dv), dtype=x.dtype, device=x.device)
         kernels.memory_output(o_raw, None, x, 2 * H * D + H * Dv, self.norm_weight, self.norm_eps, "silu", out, H, Dv)
         return self.o_proj(out, residual=residual)
@@ -130,8 +149,7 @@ class MLSTM(_MatrixMemory):
         kernels.row_dots(h, self.gate_rows, self.gate_bias, gates)
         o_raw = torch.empty((n, H, Dv + 1), dtype=torch.float32, device=x.device)
         m_exp = torch.empty((n, H), dtype=torch.float32, device=x.device)
-        kernels.memory_scan(x, 0, H * D, 2 * H * D, None, gates, self.gate_cap, float(D) ** -0.5, stop.state, ctx.cu_q, ctx.slot_ids, o_raw,
-                            m_exp, ctx.n_seqs, H, D, Dv)
+        self._scan(ctx, x, None, gates, self.gate_cap, stop, o_raw, m_exp)
         out = torch.empty((n, H * Dv), dtype=x.dtype, device=x.device)
         kernels.memory_output(o_raw, m_exp, x, 2 * H * D + H * Dv, self.norm_weight, self.norm_eps, "sigmoid", out, H, Dv)
         return self.o_proj(out, residual=residual)

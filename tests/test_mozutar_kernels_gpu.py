@@ -113,7 +113,10 @@ def test_queries_and_keys_normed_turned_and_cached(dtype, nq, nkv, dk, dims):
         x = plain.rms_unit(x, 1e-5) * npy(weight)
         return np.stack([plain.rotate_halves(x[i:i + 1], dims, 300.0, positions[i:i + 1])[0] for i in range(n)]) if dims else x
 
-    tol = 1e-5 if dtype == torch.float32 else 4e-2
+    # float32: an angle of position 4093 carries 4093 times the rounding of its frequency (3e-4), on entries up to 10
+    tol = 2e-3 if dtype == torch.float32 else 8e-2
+    near = positions < 100
+    assert np.abs(npy(qk).reshape(n, nq + nkv, dk)[near, :nq] - turned(raw[:, :nq], qw)[near]).max() < (2e-5 if dtype == torch.float32 else 8e-2)
     assert np.abs(npy(qk).reshape(n, nq + nkv, dk)[:, :nq] - turned(raw[:, :nq], qw)).max() < tol
     want_k = turned(raw[:, nq:], kw)
     page_of, at = (slots // page).long(), (slots % page).long()
@@ -268,11 +271,13 @@ def memory_reference(kind, x, gates_or_decay, heads, dim, vdim, cap, eps, weight
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("kind", ["gla", "mlstm"])
 @pytest.mark.parametrize("heads,dim,vdim", [(3, 16, 24), (2, 64, 32), (5, 12, 10), (2, 128, 128), (1, 40, 8), (2, 10, 14), (1, 256, 64), (6, 48, 64)])
-def test_memories_in_portions_with_state(dtype, kind, heads, dim, vdim):
+@pytest.mark.parametrize("chunked", [True, False])
+def test_memories_in_portions_with_state(dtype, kind, heads, dim, vdim, chunked):
     """Two requests of unequal length in five steps (portions of 1, 2 and hundreds of tokens, the second request
     absent from a step), in slots 2 and 0 of three; then a third request in the slot the second one left, cleared as
     the cache manager clears it.  The state carries S (and the normaliser and the maximum); the result is the whole
-    sequence's.  Gated linear attention: channel 0 of every head never decays (what token 0 wrote there is read
+    sequence's.  ``chunked``: the long run is cut into chunks walked in parallel (with the short run of the same step
+    walked whole beside them), else everything is walked token by token.  Gated linear attention: channel 0 of every head never decays (what token 0 wrote there is read
     hundreds of tokens on, by a query that looks at that channel alone) and channel 1 forgets at once.  mLSTM: the
     gates' pre-activations reach far beyond the cap; the first tokens' input gates lie below 0, so the maximum stays
     at the 0 it starts from and exp(-m) = 1 decides the divisor; token 40 of the long request has the largest input
@@ -316,8 +321,14 @@ def test_memories_in_portions_with_state(dtype, kind, heads, dim, vdim):
         n = rows.shape[0]
         o_raw = torch.empty(n, heads, vdim + extra, device=DEV)
         m_exp = torch.empty(n, heads, device=DEV) if extra else None
-        kernels.memory_scan(rows, 0, heads * dim, 2 * heads * dim, None if extra else side, side if extra else None, cap if extra else 0.0,
-                            dim ** -0.5, state, cu, slots, o_raw, m_exp, len(names), heads, dim, vdim)
+        first, runs, second = kernels.plan_memory([step[k] for k in names])     # the run of 260 tokens goes in five chunks, the last of 4 tokens
+        assert bool(first) == (max(step.values()) >= 128)
+        args = (rows, 0, heads * dim, 2 * heads * dim, None if extra else side, side if extra else None, cap if extra else 0.0, dim ** -0.5, state)
+        if first and chunked:
+            kernels.memory_scan_chunked(*args, slots, o_raw, m_exp, i32(first).reshape(-1), i32(runs).reshape(-1), i32(second).reshape(-1),
+                                        heads, dim, vdim)
+        else:
+            kernels.memory_scan(*args, cu, slots, o_raw, m_exp, len(names), heads, dim, vdim)
         out = torch.empty(n, heads * vdim, dtype=dtype, device=DEV)
         kernels.memory_output(o_raw, m_exp, rows, 2 * heads * dim + heads * vdim, norm_weight, eps, "sigmoid" if extra else "silu", out, heads, vdim)
         at = 0
@@ -339,13 +350,14 @@ def test_memories_in_portions_with_state(dtype, kind, heads, dim, vdim):
 @pytest.mark.parametrize("experts,identity,groups,keep,top", [(6, 2, 4, 2, 3), (8, 0, 1, 1, 2), (5, 1, 3, 2, 2), (3, 3, 2, 1, 1), (4, 4, 4, 3, 3),
                                                             (14, 2, 4, 2, 4), (60, 4, 8, 4, 6), (1, 0, 1, 1, 1)])
 def test_router_against_the_plain_one(experts, identity, groups, keep, top):
-    """Softmax over all outputs; corrections as large as the scores, some of them so negative that every choice score
-    of a group is below zero (a masked group must count as minus infinity, not as 0); the weights are the plain scores."""
+    """Softmax over all outputs; corrections as large as the scores and negative, so that most choice scores are below
+    zero (a masked group must count as minus infinity, not as 0); the weights are the plain scores.  Groups can only
+    change a choice where more are chosen than groups are kept."""
     g = torch.Generator(device=DEV).manual_seed(8)
     n, hidden, outputs = 400, 72, experts + identity
     h = torch.randn(n, hidden, generator=g, device=DEV)
-    router = torch.randn(outputs, hidden, generator=g, device=DEV) * 0.3
-    correction = torch.randn(outputs, generator=g, device=DEV) * 0.3 - 0.4
+    router = torch.randn(outputs, hidden, generator=g, device=DEV) * 0.25
+    correction = torch.randn(outputs, generator=g, device=DEV) * 0.1 - 0.3
     idx, w = torch.empty(n, top, dtype=torch.int32, device=DEV), torch.empty(n, top, device=DEV)
     counts = torch.zeros(experts, dtype=torch.int32, device=DEV)
     kernels.moe_route_softmax(h, router, correction, experts, top, groups, keep, idx, w, counts)
@@ -358,7 +370,7 @@ def test_router_against_the_plain_one(experts, identity, groups, keep, top):
     assert np.abs(by_expert(got, npy(w))[rows] - by_expert(chosen, weights)[rows]).max() < 2e-6
     assert (npy(w).sum(axis=1) < 1.0 + 1e-6).all()               # plain scores, not renormalised
     assert np.array_equal(counts.cpu().numpy(), np.bincount(got.reshape(-1), minlength=outputs)[:experts])
-    if groups > 1:
+    if top > keep and groups > 1:
         free, _ = plain.route(npy(h), npy(router), npy(correction), {"top": top})
         assert (np.sort(free, axis=1) != np.sort(chosen, axis=1)).any()         # the groups decide some of the choices
     none, _ = plain.route(npy(h), npy(router), 0.0 * npy(correction), {"top": top, "groups": {"count": groups, "keep": keep}})
