@@ -453,14 +453,31 @@ Q25_EXPORT int q25_softcap(float* logits, long long total, float cap, void* s) {
 
 // ---- layer norm around the residual stream; several branches into one update; a stream that is mixed with another ----
 
-// (v - mean) / sqrt(var + eps) over the row_len floats of `row` (shared memory), var the mean of the squared
+// (v - mean) / sqrt(var + eps) over the `hidden` floats of `row` (shared memory), var the mean of the squared
 // deviations: two passes, each a block sum in a fixed order.  Returns (mean, 1 / sqrt(var + eps)) to every thread.
+// VEC: four channels at a time (hidden is a multiple of 4).
+template <bool VEC>
 __device__ __forceinline__ float2 row_mean_inv(const float* row, int hidden, float eps, float* scratch) {
   float s = 0.f;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) s += row[c];
+  if (VEC) {
+    for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(row + c);
+      s += (v.x + v.y) + (v.z + v.w);
+    }
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) s += row[c];
+  }
   const float mean = block_sum(s, scratch) / (float)hidden;
   float q = 0.f;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) { const float d = row[c] - mean; q = fmaf(d, d, q); }
+  if (VEC) {
+    for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(row + c);
+      const float d0 = v.x - mean, d1 = v.y - mean, d2 = v.z - mean, d3 = v.w - mean;
+      q += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+    }
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) { const float d = row[c] - mean; q = fmaf(d, d, q); }
+  }
   const float var = block_sum(q, scratch) / (float)hidden;
   return make_float2(mean, 1.0f / sqrtf(var + eps));
 }
@@ -468,7 +485,7 @@ __device__ __forceinline__ float2 row_mean_inv(const float* row, int hidden, flo
 // x += post(delta); out = ((x - mean) / sqrt(var + eps)) * w + b.  post(delta), when dw is given, is the layer norm of
 // the update with weight dw and bias db, times the vector ds when that is given (a learned scale per channel); without dw
 // the update is added as it is.  With `rows` only those rows are produced and x is left alone.  out == nullptr: only the addition.
-template <typename T>
+template <typename T, bool VEC>
 __global__ void add_layernorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ dw,
                                      const float* __restrict__ db, const float* __restrict__ ds, float d_eps,
                                      const float* __restrict__ w, const float* __restrict__ b, float eps,
@@ -482,32 +499,78 @@ __global__ void add_layernorm_kernel(float* __restrict__ x, const T* __restrict_
   const int r = blockIdx.x;
   const int row = rows ? rows[r] : r;
   float* xr = x + (size_t)row * hidden;
+  constexpr int STEP = VEC ? 4 : 1;
+  const int c0 = threadIdx.x * STEP, dc = blockDim.x * STEP;
   if (delta) {
     const T* dr = delta + (size_t)row * hidden;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) d_cache[c] = to_f32(dr[c]);
     float2 st = make_float2(0.f, 1.f);
     if (dw) {
-      __syncthreads();
-      st = row_mean_inv(d_cache, hidden, d_eps, scratch);
-    }
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-      float d = d_cache[c];
-      if (dw) {
-        d = (d - st.x) * st.y * dw[c] + db[c];
-        if (ds) d *= ds[c];
+      for (int c = c0; c < hidden; c += dc) {
+        if (VEC) *reinterpret_cast<float4*>(d_cache + c) = load4<T>(dr + c);
+        else d_cache[c] = to_f32(dr[c]);
       }
-      const float v = xr[c] + d;
-      row_cache[c] = v;
-      if (!rows) xr[c] = v;
+      __syncthreads();
+      st = row_mean_inv<VEC>(d_cache, hidden, d_eps, scratch);
+    }
+    for (int c = c0; c < hidden; c += dc) {
+      if (VEC) {
+        float4 d = dw ? *reinterpret_cast<const float4*>(d_cache + c) : load4<T>(dr + c);
+        if (dw) {
+          const float4 ww = *reinterpret_cast<const float4*>(dw + c), bb = *reinterpret_cast<const float4*>(db + c);
+          d.x = (d.x - st.x) * st.y * ww.x + bb.x; d.y = (d.y - st.x) * st.y * ww.y + bb.y;
+          d.z = (d.z - st.x) * st.y * ww.z + bb.z; d.w = (d.w - st.x) * st.y * ww.w + bb.w;
+          if (ds) {
+            const float4 ss = *reinterpret_cast<const float4*>(ds + c);
+            d.x *= ss.x; d.y *= ss.y; d.z *= ss.z; d.w *= ss.w;
+          }
+        }
+        float4 v = *reinterpret_cast<const float4*>(xr + c);
+        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        *reinterpret_cast<float4*>(row_cache + c) = v;
+        if (!rows) *reinterpret_cast<float4*>(xr + c) = v;
+      } else {
+        float d = dw ? d_cache[c] : to_f32(dr[c]);
+        if (dw) {
+          d = (d - st.x) * st.y * dw[c] + db[c];
+          if (ds) d *= ds[c];
+        }
+        const float v = xr[c] + d;
+        row_cache[c] = v;
+        if (!rows) xr[c] = v;
+      }
     }
   } else {
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) row_cache[c] = xr[c];
+    for (int c = c0; c < hidden; c += dc) {
+      if (VEC) *reinterpret_cast<float4*>(row_cache + c) = *reinterpret_cast<const float4*>(xr + c);
+      else row_cache[c] = xr[c];
+    }
   }
   if (!out) return;
   __syncthreads();
-  const float2 st = row_mean_inv(row_cache, hidden, eps, scratch);
+  const float2 st = row_mean_inv<VEC>(row_cache, hidden, eps, scratch);
   T* o = out + (size_t)r * hidden;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = from_f32<T>((row_cache[c] - st.x) * st.y * w[c] + b[c]);
+  for (int c = c0; c < hidden; c += dc) {
+    if (VEC) {
+      const float4 v = *reinterpret_cast<const float4*>(row_cache + c), ww = *reinterpret_cast<const float4*>(w + c),
+                   bb = *reinterpret_cast<const float4*>(b + c);
+      store4<T>(o + c, make_float4((v.x - st.x) * st.y * ww.x + bb.x, (v.y - st.x) * st.y * ww.y + bb.y, (v.z - st.x) * st.y * ww.z + bb.z,
+                                   (v.w - st.x) * st.y * ww.w + bb.w));
+    } else {
+      o[c] = from_f32<T>((row_cache[c] - st.x) * st.y * w[c] + b[c]);
+    }
+  }
+}
+
+template <typename T, bool VEC>
+static int add_layernorm_shape(float* x, const void* delta, const float* dw, const float* db, const float* ds, float d_eps, const float* w,
+                               const float* b, float eps, void* out, const int* rows, int n_out, int hidden, size_t smem, void* stream) {
+  if (smem > 48 * 1024) {
+    const cudaError_t e = cudaFuncSetAttribute(add_layernorm_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  launch(add_layernorm_kernel<T, VEC>, dim3(n_out), dim3(hidden >= 1024 ? 256 : 128), smem, (cudaStream_t)stream, x, (const T*)delta, dw, db,
+         ds, d_eps, w, b, eps, (T*)out, rows, hidden);
+  return launch_status();
 }
 
 template <typename T>
@@ -518,13 +581,8 @@ static int add_layernorm(float* x, const void* delta, const float* dw, const flo
   if (dw && !db) return (int)cudaErrorInvalidValue;
   const size_t smem = (size_t)(2 * hidden + 32) * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-  if (smem > 48 * 1024) {
-    const cudaError_t e = cudaFuncSetAttribute(add_layernorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
-  launch(add_layernorm_kernel<T>, dim3(n_out), dim3(hidden >= 1024 ? 256 : 128), smem, (cudaStream_t)stream, x, (const T*)delta, dw, db,
-         ds, d_eps, w, b, eps, (T*)out, rows, hidden);
-  return launch_status();
+  if (hidden % 8 == 0) return add_layernorm_shape<T, true>(x, delta, dw, db, ds, d_eps, w, b, eps, out, rows, n_out, hidden, smem, stream);
+  return add_layernorm_shape<T, false>(x, delta, dw, db, ds, d_eps, w, b, eps, out, rows, n_out, hidden, smem, stream);
 }
 Q25_EXPORT int q25_add_layernorm_f32(float* x, const void* d, const float* dw, const float* db, const float* ds, float de, const float* w, const float* b, float eps, void* o, const int* rows, int n, int h, void* s) { return add_layernorm<float>(x, d, dw, db, ds, de, w, b, eps, o, rows, n, h, s); }
 Q25_EXPORT int q25_add_layernorm_bf16(float* x, const void* d, const float* dw, const float* db, const float* ds, float de, const float* w, const float* b, float eps, void* o, const int* rows, int n, int h, void* s) { return add_layernorm<bf16>(x, d, dw, db, ds, de, w, b, eps, o, rows, n, h, s); }

@@ -38,12 +38,14 @@
 
 #define GM_TOKENS 16
 #define GM_COLS 32
+#define GM_FOLD 8           // chunks whose sums a thread of the fold asks for at once
 
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
 // decay[n, c] = sigmoid(z)^(1 / tau), z = bias[c] + sum_r a2t[r, c] * low[n, r]: the low-rank projection's second
 // factor (transposed, float), the bias and the map into (0, 1) in one pass; computed as exp(log sigmoid(z) / tau).
-// A block takes 8 tokens, so that a column of a2t read from cache serves eight of them.
+// A block takes 8 tokens and as many channels as it has threads, so that a column of a2t read from cache serves
+// eight tokens.
 template <typename T>
 __global__ void gla_decay_kernel(const T* __restrict__ x, int x_stride, int low_off, int rank, const float* __restrict__ a2t,
                                  const float* __restrict__ bias, float inv_tau, float* __restrict__ decay, int n_tokens, int channels) {
@@ -56,7 +58,7 @@ __global__ void gla_decay_kernel(const T* __restrict__ x, int x_stride, int low_
     low_s[i] = n0 + t < n_tokens ? to_f32(x[(size_t)(n0 + t) * x_stride + low_off + r]) : 0.f;
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
     float z[8];
     const float b = bias ? bias[c] : 0.f;
 #pragma unroll
@@ -278,24 +280,42 @@ __global__ void __launch_bounds__(256) memory_fold_kernel(MemoryArgs p, const in
   float* st = p.state + ((size_t)p.slot_ids[run[0]] * p.H + head) * st_floats;
   float s = st[e];                                        // row D (per head): m, a copy in every column
   float m = PER_HEAD ? st[(size_t)p.D * cols] : 0.f;
-  for (int c = 0; c < n_chunks; ++c) {
-    float* sc = p.scratch + ((size_t)(first + c) * p.H + head) * st_floats;
-    const float local = sc[e];
-    if (PER_HEAD) {
-      const float* ax = p.aux + ((size_t)(first + c) * p.H + head) * 2;
-      const float f = ax[0], m_local = ax[1];
-      const float m_new = fmaxf(f + m, m_local);
-      if (r == p.D) {
-        sc[e] = m;
-        s = m_new;
+  // GM_FOLD chunks at a time: their sums and factors are asked for together, before the first state is written over a
+  // sum, so that a thread has that many loads in flight
+  for (int c0 = 0; c0 < n_chunks; c0 += GM_FOLD) {
+    float local[GM_FOLD], f0[GM_FOLD], f1[GM_FOLD];
+#pragma unroll
+    for (int i = 0; i < GM_FOLD; ++i) {
+      const int c = min(c0 + i, n_chunks - 1);
+      local[i] = p.scratch[((size_t)(first + c) * p.H + head) * st_floats + e];
+      if (PER_HEAD) {
+        const float* ax = p.aux + ((size_t)(first + c) * p.H + head) * 2;
+        f0[i] = ax[0]; f1[i] = ax[1];
       } else {
-        sc[e] = s;
-        s = fmaf(expf(f + m - m_new), s, expf(m_local - m_new) * local);
+        f0[i] = r < p.D ? p.aux[((size_t)(first + c) * p.H + head) * p.D + r] : 0.f;
+        f1[i] = 0.f;
       }
-      m = m_new;
-    } else {
-      sc[e] = s;
-      s = fmaf(p.aux[((size_t)(first + c) * p.H + head) * p.D + r], s, local);
+    }
+#pragma unroll
+    for (int i = 0; i < GM_FOLD; ++i) {
+      if (c0 + i < n_chunks) {
+        float* sc = p.scratch + ((size_t)(first + c0 + i) * p.H + head) * st_floats;
+        if (PER_HEAD) {
+          const float f = f0[i], m_local = f1[i];
+          const float m_new = fmaxf(f + m, m_local);
+          if (r == p.D) {
+            sc[e] = m;
+            s = m_new;
+          } else {
+            sc[e] = s;
+            s = fmaf(expf(f + m - m_new), s, expf(m_local - m_new) * local[i]);
+          }
+          m = m_new;
+        } else {
+          sc[e] = s;
+          s = fmaf(f0[i], s, local[i]);
+        }
+      }
     }
   }
   st[e] = s;
@@ -333,7 +353,8 @@ static int gla_decay(const void* x, int x_stride, int low_off, int rank, const f
                      int n_tokens, int channels, void* stream) {
   if (n_tokens <= 0) return 0;
   if (rank <= 0 || rank > 1024 || !(tau > 0.f)) return (int)cudaErrorInvalidValue;
-  launch(gla_decay_kernel<T>, dim3((n_tokens + 7) / 8), dim3(channels >= 256 ? 256 : 128), (size_t)8 * rank * sizeof(float), (cudaStream_t)stream,
+  const int threads = channels >= 256 ? 256 : 128;
+  launch(gla_decay_kernel<T>, dim3((n_tokens + 7) / 8, (channels + threads - 1) / threads), dim3(threads), (size_t)8 * rank * sizeof(float), (cudaStream_t)stream,
          (const T*)x, x_stride, low_off, rank, a2t, bias, 1.0f / tau, decay, n_tokens, channels);
   return launch_status();
 }
