@@ -40,6 +40,15 @@
 #define GM_COLS 32
 #define GM_FOLD 8           // chunks whose sums a thread of the fold asks for at once
 
+// Four consecutive channels as floats (bf16: 8 bytes, float: 16 bytes at a time).
+template <typename T> __device__ __forceinline__ float4 gm_load4(const T* p);
+template <> __device__ __forceinline__ float4 gm_load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 gm_load4<bf16>(const bf16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
 // decay[n, c] = sigmoid(z)^(1 / tau), z = bias[c] + sum_r a2t[r, c] * low[n, r]: the low-rank projection's second
@@ -149,6 +158,8 @@ __global__ void memory_scan_kernel(MemoryArgs p) {
     st = p.state + ((size_t)p.slot_ids[seq] * p.H + head) * st_floats;
   }
   const int chunk = p.items ? p.items[5 * seq + 3] : 0;
+  // every row of a head is whole and starts where four channels can be read at once
+  const bool vec = Dp == p.D && !((p.x_stride | p.q_off | p.k_off | p.D) & 3) && !((uintptr_t)p.x & 15) && !((uintptr_t)p.decay & 15);
   const T* x = (const T*)p.x;
 
   float S[RPT];
@@ -166,13 +177,30 @@ __global__ void memory_scan_kernel(MemoryArgs p) {
   for (int t0 = begin; t0 < end; t0 += GM_TOKENS) {
     const int nt = min(GM_TOKENS, end - t0);
     __syncthreads();                                     // the chunk before has been read out
-    for (int i = tid; i < nt * Dp; i += n_threads) {
-      const int t = i / Dp, r = i % Dp;
-      const size_t row = (size_t)(t0 + t) * p.x_stride;
-      const bool ok = r < p.D;
-      if (!LOCAL) q_s[i] = ok ? to_f32(x[row + p.q_off + head * p.D + r]) * p.q_scale : 0.f;
-      k_s[i] = ok ? to_f32(x[row + p.k_off + head * p.D + r]) : 0.f;
-      if (!PER_HEAD) a_s[i] = ok ? p.decay[((size_t)(t0 + t) * p.H + head) * p.D + r] : 0.f;
+    if (vec) {
+      // four channels a load
+      const int per_row = Dp >> 2;
+      for (int i = tid; i < nt * per_row; i += n_threads) {
+        const int t = i / per_row, r = (i - t * per_row) << 2;
+        const size_t row = (size_t)(t0 + t) * p.x_stride + head * p.D + r;
+        if (!LOCAL) {
+          float4 q = gm_load4<T>(x + row + p.q_off);
+          q.x *= p.q_scale; q.y *= p.q_scale; q.z *= p.q_scale; q.w *= p.q_scale;
+          *reinterpret_cast<float4*>(q_s + t * Dp + r) = q;
+        }
+        *reinterpret_cast<float4*>(k_s + t * Dp + r) = gm_load4<T>(x + row + p.k_off);
+        if (!PER_HEAD)
+          *reinterpret_cast<float4*>(a_s + t * Dp + r) = *reinterpret_cast<const float4*>(p.decay + ((size_t)(t0 + t) * p.H + head) * p.D + r);
+      }
+    } else {
+      for (int i = tid; i < nt * Dp; i += n_threads) {
+        const int t = i / Dp, r = i % Dp;
+        const size_t row = (size_t)(t0 + t) * p.x_stride;
+        const bool ok = r < p.D;
+        if (!LOCAL) q_s[i] = ok ? to_f32(x[row + p.q_off + head * p.D + r]) * p.q_scale : 0.f;
+        k_s[i] = ok ? to_f32(x[row + p.k_off + head * p.D + r]) : 0.f;
+        if (!PER_HEAD) a_s[i] = ok ? p.decay[((size_t)(t0 + t) * p.H + head) * p.D + r] : 0.f;
+      }
     }
     for (int i = tid; i < nt * GM_COLS; i += n_threads) {
       const int t = i / GM_COLS, c = col0 + i % GM_COLS;
