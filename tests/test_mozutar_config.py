@@ -167,3 +167,24 @@ def test_known_architectures_include_the_design():
 
     assert "Mozutar" in set(known_architectures())
     assert all(c["architecture"] == "Mozutar" for c in (M1, M2, M3, M4))
+
+
+def test_command_line_writes_a_random_model_of_the_design(tmp_path):
+    """``random-model`` resolves the design through the registry; without a rank in the file the decay's projection
+    gets the size random weights take for a size the checkpoint decides, and the folder loads into the plain model."""
+    import json
+
+    from qwen25vl_lite import cli
+
+    raw = copy.deepcopy(M3)
+    for layer in raw["layers"]:
+        if layer["type"] == "parallel":
+            del layer["mixer"]["right"]["rank"]
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(raw))
+    out = tmp_path / "model"
+    assert cli.main(["random-model", "--config", str(cfg), "--out", str(out), "--seed", "4"]) == 0
+    assert json.loads((out / "config.json").read_text())["architecture"] == "Mozutar"
+    config, w = plain.load_model_dir(str(out))
+    assert w["l0.mix.right.a1"].shape[0] == w["l0.mix.right.a2"].shape[1] > 0
+    assert np.isfinite(plain.forward_logits(config, w, [1, 2, 3])).all()
