@@ -7,3 +7,4 @@ from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry  # noqa: F401
 from .text_config import ConfigError, Qwen25VLTextConfig, read_config_json  # noqa: F401
 from .rirulix_config import RirulixConfig  # noqa: F401
 from .labolix_config import LabolixConfig  # noqa: F401
+from .fatilix_config import FatilixConfig  # noqa: F401

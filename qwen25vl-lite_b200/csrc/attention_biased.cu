@@ -7,6 +7,9 @@
 //   query i sees key j when j <= i and (i - j < window or j < keep_first)       (window 0: all j <= i)
 //   o_i = softmax_j(score) v_j;  query head h reads kv head h / (nq / nkv)
 //   sink[h] (optional): a score without key or value that joins the softmax's denominator
+//   dist_bias (optional): a learned table [dist_rows, nq]; score(i, j) += dist_bias[min(i - j, dist_rows - 1), h]
+//   gate_off (optional): the token's row holds nq * dv gate channels from that offset on, and
+//                        o_i <- o_i * sigmoid(gate_i) channel by channel (an output gate)
 //   v_row (optional): values that lie inside the key rows (a latent cache): channels between value rows
 //
 // and the write of a step's keys and values into their pages, where the values may first be mixed
@@ -28,7 +31,8 @@ __global__ void biased_attention_generic_kernel(
     const T* __restrict__ vpages, const int* __restrict__ block_table, int table_width,
     const int* __restrict__ token_seq, const int* __restrict__ cu_q, const int* __restrict__ q_start_pos,
     int n_tokens, int nq, int nkv, int dk, int dv, int page_size, int window, int keep_first, float scale,
-    const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ sink, int v_row, float softcap) {
+    const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ sink, int v_row, float softcap,
+    const float* __restrict__ dist_bias, int dist_rows, int gate_off) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ __align__(16) unsigned char att_smem[];
@@ -78,6 +82,7 @@ __global__ void biased_attention_generic_kernel(
         s = dot * scale;
         if (softcap > 0.f) s = softcap * tanhf(s / softcap);      // the scaled score squashed into (-cap, cap)
         if (r1) s -= b1 * log1pf(b2 * (float)(p - key));
+        if (dist_bias) s += dist_bias[(size_t)min(p - key, dist_rows - 1) * nq + head];
       }
       const float m_new = fmaxf(m, warp_max(s));  // finite: every tile holds at least one valid key
       const float pexp = valid ? expf(s - m_new) : 0.f;
@@ -104,10 +109,15 @@ __global__ void biased_attention_generic_kernel(
   T* o = out + (size_t)token * nq * dv + (size_t)head * dv;
   if (sink) l += expf(sink[head] - m);                // a score without key or value: it only takes its share of the weight
   const float inv_l = 1.0f / l;
+  const T* gate = gate_off >= 0 ? qkv + (size_t)token * qkv_stride + gate_off + (size_t)head * dv : nullptr;
 #pragma unroll
   for (int i = 0; i < BATT_MAX_D / 32; ++i) {
     const int c = lane + 32 * i;
-    if (c < dv) o[c] = from_f32<T>(acc[i] * inv_l);
+    if (c < dv) {
+      float v = acc[i] * inv_l;
+      if (gate) v *= 1.0f / (1.0f + expf(-to_f32(gate[c])));
+      o[c] = from_f32<T>(v);
+    }
   }
 }
 
@@ -146,10 +156,11 @@ static int biased_attention_generic(const void* qkv, int qkv_stride, void* out, 
                                     const int* block_table, int table_width, const int* token_seq, const int* cu_q,
                                     const int* q_start_pos, int n_tokens, int nq, int nkv, int dk, int dv, int page_size,
                                     int window, int keep_first, float scale, const float* r1, const float* r2, const float* sink,
-                                    int v_row, float softcap, void* stream) {
+                                    int v_row, float softcap, const float* dist_bias, int dist_rows, int gate_off, void* stream) {
   if (n_tokens <= 0) return 0;
   if (v_row <= 0) v_row = dv;
-  if (dk <= 0 || dv <= 0 || dv > BATT_MAX_D || dk > 4096 || nkv <= 0 || nq % nkv || window < 0 || keep_first < 0)
+  if (dk <= 0 || dv <= 0 || dv > BATT_MAX_D || dk > 4096 || nkv <= 0 || nq % nkv || window < 0 || keep_first < 0 ||
+      (dist_bias && dist_rows < 1))
     return (int)cudaErrorInvalidValue;
   const long long items = (long long)n_tokens * nq;
   const unsigned blocks = (unsigned)((items + BATT_WARPS - 1) / BATT_WARPS);
@@ -160,7 +171,7 @@ static int biased_attention_generic(const void* qkv, int qkv_stride, void* out, 
   }
   launch(biased_attention_generic_kernel<T>, dim3(blocks), dim3(BATT_WARPS * 32), smem, (cudaStream_t)stream, (const T*)qkv,
          qkv_stride, (T*)out, (const T*)kpages, (const T*)vpages, block_table, table_width, token_seq, cu_q, q_start_pos, n_tokens,
-         nq, nkv, dk, dv, page_size, window, keep_first, scale, r1, r2, sink, v_row, softcap);
+         nq, nkv, dk, dv, page_size, window, keep_first, scale, r1, r2, sink, v_row, softcap, dist_bias, dist_rows, gate_off);
   return launch_status();
 }
 
@@ -175,13 +186,13 @@ static int kv_store_mix(void* qkv, int qkv_stride, const void* v_other, int ld_o
 
 Q25_EXPORT int q25_biased_attention_generic_f32(const void* qkv, int qs, void* out, const void* kp, const void* vp, const int* bt,
         int tw, const int* ts, const int* cu, const int* sp, int n, int nq, int nkv, int dk, int dv, int ps, int window, int keep, float scale,
-        const float* r1, const float* r2, const float* sink, int v_row, float softcap, void* s) {
-  return biased_attention_generic<float>(qkv, qs, out, kp, vp, bt, tw, ts, cu, sp, n, nq, nkv, dk, dv, ps, window, keep, scale, r1, r2, sink, v_row, softcap, s);
+        const float* r1, const float* r2, const float* sink, int v_row, float softcap, const float* db, int db_rows, int gate_off, void* s) {
+  return biased_attention_generic<float>(qkv, qs, out, kp, vp, bt, tw, ts, cu, sp, n, nq, nkv, dk, dv, ps, window, keep, scale, r1, r2, sink, v_row, softcap, db, db_rows, gate_off, s);
 }
 Q25_EXPORT int q25_biased_attention_generic_bf16(const void* qkv, int qs, void* out, const void* kp, const void* vp, const int* bt,
         int tw, const int* ts, const int* cu, const int* sp, int n, int nq, int nkv, int dk, int dv, int ps, int window, int keep, float scale,
-        const float* r1, const float* r2, const float* sink, int v_row, float softcap, void* s) {
-  return biased_attention_generic<bf16>(qkv, qs, out, kp, vp, bt, tw, ts, cu, sp, n, nq, nkv, dk, dv, ps, window, keep, scale, r1, r2, sink, v_row, softcap, s);
+        const float* r1, const float* r2, const float* sink, int v_row, float softcap, const float* db, int db_rows, int gate_off, void* s) {
+  return biased_attention_generic<bf16>(qkv, qs, out, kp, vp, bt, tw, ts, cu, sp, n, nq, nkv, dk, dv, ps, window, keep, scale, r1, r2, sink, v_row, softcap, db, db_rows, gate_off, s);
 }
 Q25_EXPORT int q25_kv_store_mix_f32(void* qkv, int qs, const void* vo, int ldo, float mix, void* kp, void* vp, const int* slot, int n,
                                     int nq, int nkv, int dk, int dv, int ps, void* s) {
@@ -193,16 +204,20 @@ Q25_EXPORT int q25_kv_store_mix_bf16(void* qkv, int qs, const void* vo, int ldo,
 }
 
 // Queries and keys unit-normed per head and turned, keys kept as values: one block per token, a warp per head.
-// Row of the token: [nq query heads | nkv key heads], dk channels each.  Every head is divided by its root mean
-// square (eps inside the root) and multiplied by wq / wk (dk numbers shared by the heads; nullptr: heads are
-// left as projected); its first 2 * half channels are then turned by the token's angles.  Queries are written
-// back in place.  Keys go to their page slot turned; with keys_as_values the key as projected (before norm and
-// rotation) is the token's value and goes to the value pages.  Statistics, weights and angles in float.
+// Row of the token: [nq query heads | nkv key heads] of dk channels each (| nkv value heads of dv channels).  Every
+// head is divided by its root mean square (eps inside the root) and multiplied by wq / wk (dk numbers shared by the
+// heads); without weights the heads are left as projected, or with unit_norm only divided.  Its first 2 * half
+// channels are then turned by the token's angles.  temp_every > 0: the token's queries are multiplied by
+// 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1), p its position (a query temperature that grows with the
+// context).  Queries are written back in place.  Keys go to their page slot normed and turned; with keys_as_values
+// the key as projected (before norm and rotation) is the token's value and goes to the value pages; with dv > 0 the
+// row's own values go there.  Statistics, weights, angles and the temperature in float.
 template <typename T>
 __global__ void qk_norm_store_kernel(T* __restrict__ qk, int qk_stride, const float* __restrict__ wq, const float* __restrict__ wk,
-                                     float eps, const float* __restrict__ angles, int half, int layout, T* __restrict__ kpages,
-                                     T* __restrict__ vpages, const int* __restrict__ kv_slot, int nq, int nkv, int dk, int page_size,
-                                     int keys_as_values) {
+                                     float eps, int unit_norm, const float* __restrict__ angles, int half, int layout,
+                                     const int* __restrict__ positions, float temp_coef, int temp_every, T* __restrict__ kpages,
+                                     T* __restrict__ vpages, const int* __restrict__ kv_slot, int nq, int nkv, int dk, int dv,
+                                     int page_size, int keys_as_values) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ __align__(16) float qkn_smem[];        // a row of dk floats per warp
@@ -212,6 +227,7 @@ __global__ void qk_norm_store_kernel(T* __restrict__ qk, int qk_stride, const fl
   const int slot = kv_slot ? kv_slot[n] : -1;
   const int page = slot / page_size, in_page = slot % page_size;
   const float* ang = half > 0 ? angles + (size_t)n * half * 2 : nullptr;
+  const float temper = temp_every > 0 ? 1.0f + temp_coef * logf((float)((positions[n] + 1) / temp_every) + 1.0f) : 1.0f;
   for (int head = warp; head < nq + nkv; head += n_warps) {
     T* row = qk + (size_t)n * qk_stride + (size_t)head * dk;
     const bool is_key = head >= nq;
@@ -225,39 +241,48 @@ __global__ void qk_norm_store_kernel(T* __restrict__ qk, int qk_stride, const fl
       vals[c] = v;
     }
     sq = warp_sum(sq);
-    if (w) {
+    if (w || unit_norm) {
       const float inv = 1.0f / sqrtf(sq / (float)dk + eps);
-      for (int c = lane; c < dk; c += 32) vals[c] = vals[c] * inv * w[c];
+      for (int c = lane; c < dk; c += 32) vals[c] = w ? vals[c] * inv * w[c] : vals[c] * inv;
     }
     __syncwarp();
     for (int c = lane; c < dk; c += 32) {
-      const T v = from_f32<T>(rotary_channel<float>(vals, c, half, layout, ang));
-      if (is_key) { if (slot >= 0) kpages[page_row * dk + c] = v; }
-      else row[c] = v;
+      const float r = rotary_channel<float>(vals, c, half, layout, ang);
+      if (is_key) { if (slot >= 0) kpages[page_row * dk + c] = from_f32<T>(r); }
+      else row[c] = from_f32<T>(r * temper);
     }
     __syncwarp();
+  }
+  if (dv > 0 && !keys_as_values && slot >= 0) {
+    const T* vrow = qk + (size_t)n * qk_stride + (size_t)(nq + nkv) * dk;
+    for (int c = threadIdx.x; c < nkv * dv; c += blockDim.x)
+      vpages[(((size_t)page * nkv + c / dv) * page_size + in_page) * dv + c % dv] = vrow[c];
   }
 }
 
 template <typename T>
-static int qk_norm_store(void* qk, int qk_stride, const float* wq, const float* wk, float eps, const float* angles, int half, int layout,
-                         void* kpages, void* vpages, const int* kv_slot, int n_tokens, int nq, int nkv, int dk, int page_size,
-                         int keys_as_values, void* stream) {
+static int qk_norm_store(void* qk, int qk_stride, const float* wq, const float* wk, float eps, int unit_norm, const float* angles, int half,
+                         int layout, const int* positions, float temp_coef, int temp_every, void* kpages, void* vpages, const int* kv_slot,
+                         int n_tokens, int nq, int nkv, int dk, int dv, int page_size, int keys_as_values, void* stream) {
   if (n_tokens <= 0) return 0;
-  if (half < 0 || 2 * half > dk || (layout != ROTARY_INTERLEAVED && layout != ROTARY_HALVES) || (half > 0 && !angles) || dk > 2048)
+  if (half < 0 || 2 * half > dk || (layout != ROTARY_INTERLEAVED && layout != ROTARY_HALVES) || (half > 0 && !angles) || dk > 2048 ||
+      temp_every < 0 || (temp_every > 0 && !positions) || dv < 0)
     return (int)cudaErrorInvalidValue;
   const int warps = 4;
   launch(qk_norm_store_kernel<T>, dim3(n_tokens), dim3(warps * 32), (size_t)warps * dk * sizeof(float), (cudaStream_t)stream, (T*)qk,
-         qk_stride, wq, wk, eps, angles, half, layout, (T*)kpages, (T*)vpages, kv_slot, nq, nkv, dk, page_size, keys_as_values);
+         qk_stride, wq, wk, eps, unit_norm, angles, half, layout, positions, temp_coef, temp_every, (T*)kpages, (T*)vpages, kv_slot, nq,
+         nkv, dk, dv, page_size, keys_as_values);
   return launch_status();
 }
-Q25_EXPORT int q25_biased_attention_qk_norm_store_f32(void* qk, int qs, const float* wq, const float* wk, float eps, const float* ang, int half, int layout,
-        void* kp, void* vp, const int* slot, int n, int nq, int nkv, int dk, int ps, int kav, void* s) {
-  return qk_norm_store<float>(qk, qs, wq, wk, eps, ang, half, layout, kp, vp, slot, n, nq, nkv, dk, ps, kav, s);
+Q25_EXPORT int q25_biased_attention_qk_norm_store_f32(void* qk, int qs, const float* wq, const float* wk, float eps, int unit, const float* ang,
+        int half, int layout, const int* pos, float tc, int te, void* kp, void* vp, const int* slot, int n, int nq, int nkv, int dk, int dv,
+        int ps, int kav, void* s) {
+  return qk_norm_store<float>(qk, qs, wq, wk, eps, unit, ang, half, layout, pos, tc, te, kp, vp, slot, n, nq, nkv, dk, dv, ps, kav, s);
 }
-Q25_EXPORT int q25_biased_attention_qk_norm_store_bf16(void* qk, int qs, const float* wq, const float* wk, float eps, const float* ang, int half, int layout,
-        void* kp, void* vp, const int* slot, int n, int nq, int nkv, int dk, int ps, int kav, void* s) {
-  return qk_norm_store<bf16>(qk, qs, wq, wk, eps, ang, half, layout, kp, vp, slot, n, nq, nkv, dk, ps, kav, s);
+Q25_EXPORT int q25_biased_attention_qk_norm_store_bf16(void* qk, int qs, const float* wq, const float* wk, float eps, int unit, const float* ang,
+        int half, int layout, const int* pos, float tc, int te, void* kp, void* vp, const int* slot, int n, int nq, int nkv, int dk, int dv,
+        int ps, int kav, void* s) {
+  return qk_norm_store<bf16>(qk, qs, wq, wk, eps, unit, ang, half, layout, pos, tc, te, kp, vp, slot, n, nq, nkv, dk, dv, ps, kav, s);
 }
 
 // ================================================================================================
@@ -298,10 +323,20 @@ struct BiasedArgs {
   const float* r2;
   const float* sink;   // per query head, a score without key or value that joins the denominator (nullptr: none)
   int v_row;           // channels between two value rows of a page (DV, or the key row's when values lie inside the keys)
+  const float* dist_bias;  // [dist_rows, nq] added to the score by distance, the last row for every distance beyond (nullptr: none)
+  int dist_rows;
+  int gate_off;        // where a token's row holds its nq * DV output-gate channels (-1: no gate)
   int n_splits;
   float* part_o;   // [items, nq, splits, DV]
   float* part_ml;  // [items, nq, splits, 2]
 };
+
+// sigmoid of two neighbouring gate channels (an even channel offset: one 32-bit load).
+__device__ __forceinline__ float2 gate_pair(const bf16* g) {
+  const float2 z = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(g));
+  return make_float2(1.0f / (1.0f + __expf(-z.x)), 1.0f / (1.0f + __expf(-z.y)));
+}
+__device__ __forceinline__ float gate_one(const bf16* g) { return 1.0f / (1.0f + __expf(-__bfloat162float(*g))); }
 
 // The tiles of keys that queries at positions p_first .. p_last walk.
 struct KeyWalk {
@@ -356,8 +391,9 @@ __device__ __forceinline__ void biased_load_tile(unsigned char* ks, unsigned cha
 template <int DK, int DV, int BN, bool FULL>
 __device__ __forceinline__ void biased_tile(const unsigned (&qf)[DK / 16][4], const unsigned char* ks, const unsigned char* vs,
                                             int key0, int rl, int rh, int p0, int p1, int window, int keep_first, float scale_log2,
-                                            float cap_log2, float scale_over_cap, float b10, float b20, float b11, float b21, float (&m)[2], float (&l)[2],
-                                            float (&o)[DV / 8][4]) {
+                                            float cap_log2, float scale_over_cap, float b10, float b20, float b11, float b21,
+                                            const float* __restrict__ tab0, const float* __restrict__ tab1, int dist_rows, int nq,
+                                            float (&m)[2], float (&l)[2], float (&o)[DV / 8][4]) {
   constexpr int PK = Tile<DK>::PITCH, PV = Tile<DV>::PITCH;
   const int lane = threadIdx.x & 31, t = lane & 3;
   float s[BN / 8][4];
@@ -374,6 +410,12 @@ __device__ __forceinline__ void biased_tile(const unsigned (&qf)[DK / 16][4], co
   // distance of the row's query to the thread's first key of the tile, as a float; the other keys
   // of the thread lie constants further on
   const float d0 = (float)(p0 - key0 - 2 * t), d1 = (float)(p1 - key0 - 2 * t);
+  // the distance table: a row whose nearest key of the tile lies at the table's last row or beyond adds one number
+  // to all its scores; the table's entries are natural-log scores, the kernel's live in the base-2 domain
+  constexpr float LOG2E = 1.4426950408889634f;
+  const int last_row = dist_rows - 1;
+  const bool far0 = tab0 && p0 - (key0 + BN - 1) >= last_row, far1 = tab0 && p1 - (key0 + BN - 1) >= last_row;
+  const float fb0 = far0 ? tab0[(size_t)last_row * nq] * LOG2E : 0.f, fb1 = far1 ? tab1[(size_t)last_row * nq] * LOG2E : 0.f;
   float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
   for (int j = 0; j < BN / 8; ++j) {
@@ -383,6 +425,14 @@ __device__ __forceinline__ void biased_tile(const unsigned (&qf)[DK / 16][4], co
       const float b1 = e < 2 ? b10 : b11, b2 = e < 2 ? b20 : b21;
       float v = cap_log2 > 0.f ? cap_log2 * tanhf(s[j][e] * scale_over_cap) - b1 * __log2f(fmaf(b2, fd, 1.0f))
                                : fmaf(s[j][e], scale_log2, -b1 * __log2f(fmaf(b2, fd, 1.0f)));
+      if (tab0) {
+        if (e < 2 ? far0 : far1) {
+          v += e < 2 ? fb0 : fb1;
+        } else {
+          const int dist = (e < 2 ? p0 : p1) - (key0 + j * 8 + 2 * t + (e & 1));
+          v = fmaf((e < 2 ? tab0 : tab1)[(size_t)min(max(dist, 0), last_row) * nq], LOG2E, v);
+        }
+      }
       if (!FULL) {
         const int kidx = key0 + j * 8 + 2 * t + (e & 1);
         const int dist = (e < 2 ? p0 : p1) - kidx;
@@ -469,6 +519,8 @@ __global__ void __launch_bounds__(128) biased_prefill_kernel(BiasedArgs a) {
   const int h0 = kvh * group + (r0 < rows ? r0 % group : 0), h1 = kvh * group + (r1 < rows ? r1 % group : 0);
   const int p0 = tok0 < 0 ? -1 : start + tok0, p1 = tok1 < 0 ? -1 : start + tok1;
   const float b10 = a.r1 ? a.r1[h0] : 0.f, b20 = a.r1 ? a.r2[h0] : 0.f, b11 = a.r1 ? a.r1[h1] : 0.f, b21 = a.r1 ? a.r2[h1] : 0.f;
+  const float* tab0 = a.dist_bias ? a.dist_bias + h0 : nullptr;
+  const float* tab1 = a.dist_bias ? a.dist_bias + h1 : nullptr;
   unsigned qf[DK / 16][4];
   load_q<DK>(qf, [&](int r) -> const bf16* {
     const int rr = tile_row0 + warp * 16 + r;
@@ -501,9 +553,9 @@ __global__ void __launch_bounds__(128) biased_prefill_kernel(BiasedArgs a) {
     __syncthreads();
     walk.tile(i, BN, key0, rl, rh);
     if (tile_is_full(key0, BN, rl, rh, wp_min, wp_max, a.window, a.keep_first))
-      biased_tile<DK, DV, BN, true>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, a.cap_log2, a.scale_over_cap, b10, b20, b11, b21, m, l, o);
+      biased_tile<DK, DV, BN, true>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, a.cap_log2, a.scale_over_cap, b10, b20, b11, b21, tab0, tab1, a.dist_rows, a.nq, m, l, o);
     else
-      biased_tile<DK, DV, BN, false>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, a.cap_log2, a.scale_over_cap, b10, b20, b11, b21, m, l, o);
+      biased_tile<DK, DV, BN, false>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, a.cap_log2, a.scale_over_cap, b10, b20, b11, b21, tab0, tab1, a.dist_rows, a.nq, m, l, o);
     __syncthreads();
   }
   float l0 = quad_sum(l[0]), l1 = quad_sum(l[1]);
@@ -512,11 +564,16 @@ __global__ void __launch_bounds__(128) biased_prefill_kernel(BiasedArgs a) {
     if (tok1 >= 0) l1 += exp2f(a.sink[h1] * 1.4426950408889634f - m[1]);
   }
   const float i0 = l0 > 0.f ? 1.0f / l0 : 0.f, i1 = l1 > 0.f ? 1.0f / l1 : 0.f;
+  const bf16* g0 = a.gate_off >= 0 && tok0 >= 0 ? a.qkv + (size_t)(first + tok0) * a.qkv_stride + a.gate_off + (size_t)h0 * DV : nullptr;
+  const bf16* g1 = a.gate_off >= 0 && tok1 >= 0 ? a.qkv + (size_t)(first + tok1) * a.qkv_stride + a.gate_off + (size_t)h1 * DV : nullptr;
 #pragma unroll
   for (int nb = 0; nb < DV / 8; ++nb) {
     const int c = nb * 8 + 2 * t;
-    if (tok0 >= 0) *reinterpret_cast<unsigned*>(a.out + (size_t)(first + tok0) * a.nq * DV + (size_t)h0 * DV + c) = pack_bf16(o[nb][0] * i0, o[nb][1] * i0);
-    if (tok1 >= 0) *reinterpret_cast<unsigned*>(a.out + (size_t)(first + tok1) * a.nq * DV + (size_t)h1 * DV + c) = pack_bf16(o[nb][2] * i1, o[nb][3] * i1);
+    float y0 = o[nb][0] * i0, y1 = o[nb][1] * i0, y2 = o[nb][2] * i1, y3 = o[nb][3] * i1;
+    if (g0) { const float2 z = gate_pair(g0 + c); y0 *= z.x; y1 *= z.y; }
+    if (g1) { const float2 z = gate_pair(g1 + c); y2 *= z.x; y3 *= z.y; }
+    if (tok0 >= 0) *reinterpret_cast<unsigned*>(a.out + (size_t)(first + tok0) * a.nq * DV + (size_t)h0 * DV + c) = pack_bf16(y0, y1);
+    if (tok1 >= 0) *reinterpret_cast<unsigned*>(a.out + (size_t)(first + tok1) * a.nq * DV + (size_t)h1 * DV + c) = pack_bf16(y2, y3);
   }
 }
 
@@ -541,6 +598,8 @@ __global__ void __launch_bounds__(128) biased_decode_kernel(BiasedArgs a) {
   const int h0 = kvh * group + (g < group ? g : 0), h1 = kvh * group + (g + 8 < group ? g + 8 : 0);
   const int p0 = g < group ? p : -1, p1 = g + 8 < group ? p : -1;
   const float b10 = a.r1 ? a.r1[h0] : 0.f, b20 = a.r1 ? a.r2[h0] : 0.f, b11 = a.r1 ? a.r1[h1] : 0.f, b21 = a.r1 ? a.r2[h1] : 0.f;
+  const float* tab0 = a.dist_bias ? a.dist_bias + h0 : nullptr;
+  const float* tab1 = a.dist_bias ? a.dist_bias + h1 : nullptr;
   unsigned qf[DK / 16][4];
   load_q<DK>(qf, [&](int r) -> const bf16* {
     return r < group ? a.qkv + (size_t)token * a.qkv_stride + (size_t)(kvh * group + r) * DK : nullptr;
@@ -571,7 +630,7 @@ __global__ void __launch_bounds__(128) biased_decode_kernel(BiasedArgs a) {
     }
     __syncwarp();
     walk.tile(i, BN, key0, rl, rh);
-    biased_tile<DK, DV, BN, false>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, a.cap_log2, a.scale_over_cap, b10, b20, b11, b21, m, l, o);
+    biased_tile<DK, DV, BN, false>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, a.cap_log2, a.scale_over_cap, b10, b20, b11, b21, tab0, tab1, a.dist_rows, a.nq, m, l, o);
     __syncwarp();
   }
   cp_async_wait<0>();
@@ -607,7 +666,9 @@ __global__ void __launch_bounds__(128) biased_decode_kernel(BiasedArgs a) {
     const int head = kvh * group + r;
     if (a.n_splits == 1) {
       if (a.sink && mm != -INFINITY) sum += exp2f(a.sink[head] * 1.4426950408889634f - mm);
-      a.out[(size_t)token * a.nq * DV + (size_t)head * DV + c] = __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+      float y = sum > 0.f ? acc / sum : 0.f;
+      if (a.gate_off >= 0) y *= gate_one(a.qkv + (size_t)token * a.qkv_stride + a.gate_off + (size_t)head * DV + c);
+      a.out[(size_t)token * a.nq * DV + (size_t)head * DV + c] = __float2bfloat16_rn(y);
     } else {
       const size_t at = ((size_t)item * a.nq + head) * a.n_splits + split;
       a.part_o[at * DV + c] = acc;
@@ -634,7 +695,9 @@ __global__ void biased_combine_kernel(BiasedArgs a) {
     acc = fmaf(a.part_o[(base + s) * DV + c], f, acc);
   }
   if (a.sink && mm != -INFINITY) sum += exp2f(a.sink[head] * 1.4426950408889634f - mm);
-  a.out[(size_t)token * a.nq * DV + (size_t)head * DV + c] = __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+  float y = sum > 0.f ? acc / sum : 0.f;
+  if (a.gate_off >= 0) y *= gate_one(a.qkv + (size_t)token * a.qkv_stride + a.gate_off + (size_t)head * DV + c);
+  a.out[(size_t)token * a.nq * DV + (size_t)head * DV + c] = __float2bfloat16_rn(y);
 }
 
 template <int DK, int DV>
@@ -683,9 +746,12 @@ Q25_EXPORT int q25_biased_attention_mma_bf16(const void* qkv, int qkv_stride, vo
                                              int tw, const int* cu, const int* sp, const int* tiles, int n_tiles, const int* items,
                                              int n_items, int nq, int nkv, int dk, int dv, int ps, int window, int keep, float scale,
                                              const float* r1, const float* r2, const float* sink, int v_row, int n_splits, float* part_o,
-                                             float* part_ml, float softcap, void* stream) {
+                                             float* part_ml, float softcap, const float* dist_bias, int dist_rows, int gate_off,
+                                             void* stream) {
   if (n_tiles <= 0 && n_items <= 0) return 0;
-  if (nkv <= 0 || nq % nkv || ps <= 0 || n_splits < 1 || (n_items > 0 && nq / nkv > 16) || v_row % 8) return (int)cudaErrorInvalidValue;
+  if (nkv <= 0 || nq % nkv || ps <= 0 || n_splits < 1 || (n_items > 0 && nq / nkv > 16) || v_row % 8 || (dist_bias && dist_rows < 1) ||
+      (gate_off >= 0 && gate_off % 2))
+    return (int)cudaErrorInvalidValue;
   BiasedArgs a;
   a.qkv = (const bf16*)qkv; a.qkv_stride = qkv_stride; a.out = (bf16*)out; a.kpages = (const bf16*)kp; a.vpages = (const bf16*)vp;
   a.block_table = bt; a.table_width = tw; a.cu_q = cu; a.q_start_pos = sp; a.items = nullptr;
@@ -693,6 +759,7 @@ Q25_EXPORT int q25_biased_attention_mma_bf16(const void* qkv, int qkv_stride, vo
   a.scale_log2 = scale * 1.4426950408889634f;
   a.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f; a.scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
   a.r1 = r1; a.r2 = r2; a.sink = sink; a.v_row = v_row > 0 ? v_row : dv; a.n_splits = n_splits; a.part_o = part_o; a.part_ml = part_ml;
+  a.dist_bias = dist_bias; a.dist_rows = dist_bias ? dist_rows : 1; a.gate_off = gate_off;
   cudaStream_t s = (cudaStream_t)stream;
 #define BIASED_CASE(K, V) if (dk == K && dv == V) return biased_mma_launch<K, V>(a, n_tiles, n_items, tiles, items, s);
   BIASED_SIZES(BIASED_CASE)

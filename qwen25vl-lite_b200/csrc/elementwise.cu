@@ -147,13 +147,14 @@ __device__ __forceinline__ void group_inverse_rms(const float* row_cache, int hi
 
 #define NORM_MAX_GROUPS 64
 
-// x[n,:] = norm_in_groups(E[token[n],:] + P[position[n],:]) * w: a token embedding with a learned
-// vector per position added before the model's norm; the float32 residual stream starts here.
+// x[n,:] = norm_in_groups(E[token[n],:] * scale + P[position[n],:]) * w: a token embedding with a learned
+// vector per position (not scaled) added before the model's norm; w == nullptr: no norm, the sum as it
+// is.  The float32 residual stream starts here.
 template <typename T, bool EXACT>
 __global__ void embed_position_norm_kernel(const T* __restrict__ table, const T* __restrict__ pos_table,
                                            const int* __restrict__ ids, const int* __restrict__ positions,
                                            const float* __restrict__ w, float eps, float* __restrict__ x, int hidden,
-                                           int vocab, int max_positions, int groups) {
+                                           int vocab, int max_positions, int groups, float scale) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ __align__(16) float row_cache[];  // hidden floats + 32 scratch + groups
@@ -165,7 +166,12 @@ __global__ void embed_position_norm_kernel(const T* __restrict__ table, const T*
   p = p < 0 ? 0 : (p >= max_positions ? max_positions - 1 : p);
   const T* e = table + (size_t)id * hidden;
   const T* q = pos_table + (size_t)p * hidden;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) row_cache[c] = to_f32(e[c]) + to_f32(q[c]);
+  float* dst0 = x + (size_t)row * hidden;
+  if (!w) {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst0[c] = fmaf(to_f32(e[c]), scale, to_f32(q[c]));
+    return;
+  }
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) row_cache[c] = fmaf(to_f32(e[c]), scale, to_f32(q[c]));
   __syncthreads();
   group_inverse_rms<EXACT>(row_cache, hidden, groups, eps, inv, scratch);
   const int width = hidden / groups;
@@ -176,7 +182,8 @@ __global__ void embed_position_norm_kernel(const T* __restrict__ table, const T*
 // x[row] += d, where d = delta[row] as it is (dw == nullptr) or norm_in_groups(delta[row]) * dw (a
 // sublayer that is normalised after as well as before); then out[r] = norm_in_groups(x[row]) * w.
 // rows as in add_rmsnorm_kernel: with rows the sum is formed for those rows only and x is left alone.
-// out == nullptr: only the addition.
+// out == nullptr: only the addition.  w == nullptr: out[r] = x[row] as it is, in T (a sublayer that reads
+// the stream itself).
 template <typename T, bool EXACT, bool VEC>
 __global__ void add_norm_groups_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ dw,
                                        float d_eps, int d_groups, const float* __restrict__ w, float eps, int groups,
@@ -228,9 +235,16 @@ __global__ void add_norm_groups_kernel(float* __restrict__ x, const T* __restric
     }
   }
   if (!out) return;
+  T* o = out + (size_t)r * hidden;
+  if (!w) {            // every thread reads back what it wrote itself
+    for (int c = threadIdx.x * STEP; c < hidden; c += blockDim.x * STEP) {
+      if (VEC) store4<T>(o + c, *reinterpret_cast<const float4*>(row_cache + c));
+      else o[c] = from_f32<T>(row_cache[c]);
+    }
+    return;
+  }
   group_inverse_rms<EXACT>(row_cache, hidden, groups, eps, inv, scratch);
   const int width = hidden / groups;
-  T* o = out + (size_t)r * hidden;
   for (int c = threadIdx.x * STEP; c < hidden; c += blockDim.x * STEP) {
     if (VEC) {
       const float4 v = *reinterpret_cast<const float4*>(row_cache + c), ww = *reinterpret_cast<const float4*>(w + c);
@@ -324,7 +338,7 @@ __global__ void softcap_kernel(float* __restrict__ logits, size_t total, float c
 
 template <typename T, bool EXACT>
 static int embed_position_norm(const void* table, const void* pos_table, const int* ids, const int* positions, const float* w,
-                               float eps, float* x, int n, int hidden, int vocab, int max_positions, int groups, void* stream) {
+                               float eps, float* x, int n, int hidden, int vocab, int max_positions, int groups, float scale, void* stream) {
   if (n <= 0) return 0;
   if (groups <= 0 || groups > NORM_MAX_GROUPS || hidden % groups) return (int)cudaErrorInvalidValue;
   const size_t smem = (size_t)(hidden + 32 + NORM_MAX_GROUPS) * sizeof(float);
@@ -334,7 +348,7 @@ static int embed_position_norm(const void* table, const void* pos_table, const i
     if (e != cudaSuccess) return (int)e;
   }
   launch(embed_position_norm_kernel<T, EXACT>, dim3(n), dim3(hidden >= 1024 ? 256 : 128), smem, (cudaStream_t)stream,
-         (const T*)table, (const T*)pos_table, ids, positions, w, eps, x, hidden, vocab, max_positions, groups);
+         (const T*)table, (const T*)pos_table, ids, positions, w, eps, x, hidden, vocab, max_positions, groups, scale);
   return launch_status();
 }
 
@@ -420,8 +434,8 @@ Q25_EXPORT int q25_add_rmsnorm_bf16(float* x, const void* d, const float* w, flo
 Q25_EXPORT int q25_silu_mul_f32(const void* gu, void* o, int n, int inter, int paired, void* s) { return silu_mul<float>(gu, o, n, inter, paired, s); }
 Q25_EXPORT int q25_silu_mul_bf16(const void* gu, void* o, int n, int inter, int paired, void* s) { return silu_mul<bf16>(gu, o, n, inter, paired, s); }
 
-Q25_EXPORT int q25_embed_position_norm_f32(const void* t, const void* pt, const int* ids, const int* pos, const float* w, float eps, float* x, int n, int h, int v, int mp, int g, void* s) { return embed_position_norm<float, true>(t, pt, ids, pos, w, eps, x, n, h, v, mp, g, s); }
-Q25_EXPORT int q25_embed_position_norm_bf16(const void* t, const void* pt, const int* ids, const int* pos, const float* w, float eps, float* x, int n, int h, int v, int mp, int g, void* s) { return embed_position_norm<bf16, false>(t, pt, ids, pos, w, eps, x, n, h, v, mp, g, s); }
+Q25_EXPORT int q25_embed_position_norm_f32(const void* t, const void* pt, const int* ids, const int* pos, const float* w, float eps, float* x, int n, int h, int v, int mp, int g, float sc, void* s) { return embed_position_norm<float, true>(t, pt, ids, pos, w, eps, x, n, h, v, mp, g, sc, s); }
+Q25_EXPORT int q25_embed_position_norm_bf16(const void* t, const void* pt, const int* ids, const int* pos, const float* w, float eps, float* x, int n, int h, int v, int mp, int g, float sc, void* s) { return embed_position_norm<bf16, false>(t, pt, ids, pos, w, eps, x, n, h, v, mp, g, sc, s); }
 Q25_EXPORT int q25_add_norm_groups_f32(float* x, const void* d, const float* dw, float de, int dg, const float* w, float eps, int g, void* o, const int* rows, int n, int h, void* s) { return add_norm_groups<float, true>(x, d, dw, de, dg, w, eps, g, o, rows, n, h, s); }
 Q25_EXPORT int q25_add_norm_groups_bf16(float* x, const void* d, const float* dw, float de, int dg, const float* w, float eps, int g, void* o, const int* rows, int n, int h, void* s) { return add_norm_groups<bf16, false>(x, d, dw, de, dg, w, eps, g, o, rows, n, h, s); }
 Q25_EXPORT int q25_glu_clamped_f32(const void* gu, void* o, int n, int inter, float limit, float alpha, float shift, int paired, void* s) { return glu_clamped<float>(gu, o, n, inter, limit, alpha, shift, paired, s); }
@@ -660,3 +674,29 @@ Q25_EXPORT int q25_stream_set(float* x, const float* y, const float* bias, int r
   launch(stream_set_kernel, dim3(rows), dim3(128), 0, (cudaStream_t)s, x, y, bias, h);
   return launch_status();
 }
+
+// A feed-forward's activation on its own: out = act(in) element by element, in float.  kind 0: the square of
+// relu, max(z, 0)^2; kind 1: gelu in its tanh form, 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float unary_act(float z, int kind) {
+  if (kind == 0) { const float r = fmaxf(z, 0.f); return r * r; }
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * fmaf(0.044715f * z * z, z, z)));
+}
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out, size_t total, int kind) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = from_f32<T>(unary_act(to_f32(in[i]), kind));
+}
+template <typename T>
+static int activation(const void* in, void* out, long long total, int kind, void* stream) {
+  if (total <= 0) return 0;
+  if (kind < 0 || kind > 1) return (int)cudaErrorInvalidValue;
+  size_t blocks = ((size_t)total + 255) / 256;
+  const size_t most = (size_t)(device_sm_count() > 0 ? device_sm_count() : 148) * 16;
+  if (blocks > most) blocks = most;
+  launch(activation_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)in, (T*)out, (size_t)total, kind);
+  return launch_status();
+}
+Q25_EXPORT int q25_activation_f32(const void* in, void* out, long long total, int kind, void* s) { return activation<float>(in, out, total, kind, s); }
+Q25_EXPORT int q25_activation_bf16(const void* in, void* out, long long total, int kind, void* s) { return activation<bf16>(in, out, total, kind, s); }

@@ -57,7 +57,8 @@
 
 // EPI_GLU: the clamped gated unit g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit), in the
 // layout of EPI_SWIGLU; its two constants (limit, alpha) are read where EPI_BIAS reads its bias.
-enum { EPI_STORE = 0, EPI_BIAS = 1, EPI_F32 = 2, EPI_SWIGLU = 3, EPI_RESIDUAL = 4, EPI_GLU = 5 };
+// EPI_RELU2: the square of relu, max(y, 0)^2, stored in bfloat16.
+enum { EPI_STORE = 0, EPI_BIAS = 1, EPI_F32 = 2, EPI_SWIGLU = 3, EPI_RESIDUAL = 4, EPI_GLU = 5, EPI_RELU2 = 6 };
 
 #define GC_ROWS 16
 #define GC_MAX_M 8                               // rows of x: one 8-column tile of the MMA (MT = 1).  A second tile
@@ -189,6 +190,7 @@ __device__ __forceinline__ void gc_store_group(const float (&acc)[MT][4], int gr
         if (n >= op.N) continue;
         float v = acc[mt][e + 2 * h];
         if (op.epi == EPI_BIAS) v += op.bias[n];
+        if (op.epi == EPI_RELU2) { v = fmaxf(v, 0.f); v *= v; }
         if (op.epi == EPI_F32) reinterpret_cast<float*>(op.out)[(size_t)m * op.ldo + n] = v;
         else if (op.epi == EPI_RESIDUAL) {
           float* dst = reinterpret_cast<float*>(op.out) + (size_t)m * op.ldo + n;
@@ -744,7 +746,7 @@ static bool chain_cut(const ChainOpDesc& d, ChainOp& op, int sms, int limit, int
   if (((unsigned long long)d.W & 15) || ((unsigned long long)d.X & 15)) return false;
   if (d.norm ? (d.ldx % 4 || !d.norm_w) : (d.ldx % 8 != 0)) return false;
   if (((d.epi == EPI_SWIGLU || d.epi == EPI_GLU) && d.N % 16) || ((d.epi == EPI_BIAS || d.epi == EPI_GLU) && !d.bias) || d.epi < 0 ||
-      d.epi > EPI_GLU)
+      d.epi > EPI_RELU2)
     return false;
   op.W = (const bf16*)d.W; op.X = d.X; op.norm_w = d.norm_w; op.bias = d.bias; op.out = d.out;
   op.ldx = d.ldx; op.ldo = d.ldo; op.M = d.M; op.N = d.N; op.K = d.K; op.epi = d.epi; op.norm = d.norm; op.eps = d.eps;

@@ -28,7 +28,8 @@
 
 // T5_GLU: the clamped gated unit g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit), in the
 // layout of T5_SWIGLU; its two constants (limit, alpha) are read where the other epilogues read a bias.
-enum { T5_STORE = 0, T5_BIAS = 1, T5_F32 = 2, T5_SWIGLU = 3, T5_RESIDUAL = 4, T5_GLU = 5 };
+// T5_RELU2: the square of relu, max(y, 0)^2, stored in bfloat16.
+enum { T5_STORE = 0, T5_BIAS = 1, T5_F32 = 2, T5_SWIGLU = 3, T5_RESIDUAL = 4, T5_GLU = 5, T5_RELU2 = 6 };
 
 #define T5_BM 128
 #define T5_BK 64
@@ -100,6 +101,7 @@ __device__ __forceinline__ void t5_emit32(const float (&v)[32], int m, int n, in
         for (int j = 0; j < 8; ++j) {
           float y = v[q * 8 + j];
           if constexpr (EPI == T5_BIAS) y += bias[n + q * 8 + j];
+          if constexpr (EPI == T5_RELU2) { y = fmaxf(y, 0.f); y *= y; }
           o8[j] = __float2bfloat16_rn(y);
         }
         *reinterpret_cast<uint4*>(dst + q * 8) = *reinterpret_cast<const uint4*>(o8);
@@ -108,6 +110,7 @@ __device__ __forceinline__ void t5_emit32(const float (&v)[32], int m, int n, in
       for (int j = 0; j < 32 && n + j < N; ++j) {
         float y = v[j];
         if constexpr (EPI == T5_BIAS) y += bias[n + j];
+        if constexpr (EPI == T5_RELU2) { y = fmaxf(y, 0.f); y *= y; }
         dst[j] = __float2bfloat16_rn(y);
       }
     }
@@ -605,6 +608,7 @@ Q25_EXPORT int q25_gemm_tcgen05_bf16(const void* W, const void* X, int ldx, cons
       case T5_SWIGLU: return launch_pair<T5_SWIGLU>(mx, mw, mw64, bias, out, ldo, M, N, K, err, s);
       case T5_RESIDUAL: return launch_pair<T5_RESIDUAL>(mx, mw, mw64, bias, out, ldo, M, N, K, err, s);
       case T5_GLU: return launch_pair<T5_GLU>(mx, mw, mw64, bias, out, ldo, M, N, K, err, s);
+      case T5_RELU2: return launch_pair<T5_RELU2>(mx, mw, mw64, bias, out, ldo, M, N, K, err, s);
       default: return (int)cudaErrorInvalidValue;
     }
   }
@@ -620,6 +624,7 @@ Q25_EXPORT int q25_gemm_tcgen05_bf16(const void* W, const void* X, int ldx, cons
     T5_CASE(T5_SWIGLU)
     T5_CASE(T5_RESIDUAL)
     T5_CASE(T5_GLU)
+    T5_CASE(T5_RELU2)
     default: return (int)cudaErrorInvalidValue;
   }
 #undef T5_CASE

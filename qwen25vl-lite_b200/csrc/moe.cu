@@ -73,13 +73,14 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, cons
 // which stand for experts without matrices (a choice among them takes no row of the grouped products).  The choice looks
 // at score + correction[e]; the rows form `groups` equal runs of neighbours, a run's mark is its largest such number, and
 // only the `keep` runs with the largest marks can be chosen from (the others count as minus infinity).  The `top`
-// largest are chosen (ties to the lower index, among runs too); a choice weighs in with its plain score.  counts: one per
+// largest are chosen (ties to the lower index, among runs too); a choice weighs in with its plain score: as it is, or
+// with renorm divided by the sum of the token's chosen scores (+ 1e-20); either way times weight_scale.  counts: one per
 // expert with matrices.  One block of 8 warps per TOK tokens as above, then a warp per token.
 template <typename T, int TOK>
 __global__ void __launch_bounds__(256)
 moe_route_softmax_kernel(const T* __restrict__ h, const float* __restrict__ router, const float* __restrict__ correction,
                          int* __restrict__ topk_idx, float* __restrict__ topk_w, int* __restrict__ counts, int n_tokens, int hidden,
-                         int experts, int outputs, int top, int groups, int keep) {
+                         int experts, int outputs, int top, int groups, int keep, int renorm, float weight_scale) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ __align__(16) float route_smem[];       // TOK rows of hidden floats, then TOK x 3 x (MOE_MAX_EXPERTS + 1) numbers
@@ -174,6 +175,12 @@ moe_route_softmax_kernel(const T* __restrict__ h, const float* __restrict__ rout
       }
     }
     __syncwarp();
+  }
+  if (lane == 0 && (renorm || weight_scale != 1.0f)) {         // the lane that wrote the weights: in the order of the choices
+    float* w = topk_w + (size_t)n * top;
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) sum += w[k];
+    for (int k = 0; k < top; ++k) w[k] = (renorm ? w[k] / (sum + 1e-20f) : w[k]) * weight_scale;
   }
 }
 
@@ -505,10 +512,12 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
 }
 
 // out[n, :] = sum over the token's choices, in their order, of w[pair] * (y[row of the pair, :], or the token's own
-// input h[n, :] when the pair has no row: a choice that stands for an expert without matrices), in T.
+// input h[n, :] when the pair has no row: a choice that stands for an expert without matrices), plus shared[n, :] when
+// given (an expert that every token uses, unweighted), in T.
 template <typename T>
 __global__ void moe_combine_weighted_kernel(const float* __restrict__ y, const int* __restrict__ pair_row, const float* __restrict__ topk_w,
-                                            const T* __restrict__ h, T* __restrict__ out, int n_tokens, int hidden, int top) {
+                                            const T* __restrict__ h, const T* __restrict__ shared, T* __restrict__ out, int n_tokens,
+                                            int hidden, int top) {
   pdl_trigger();
   pdl_wait();
   const int n = blockIdx.x;
@@ -525,6 +534,7 @@ __global__ void moe_combine_weighted_kernel(const float* __restrict__ y, const i
       const float v = rows[k] >= 0 ? y[(size_t)rows[k] * hidden + c] : to_f32(h[(size_t)n * hidden + c]);
       acc = fmaf(ws[k], v, acc);
     }
+    if (shared) acc += to_f32(shared[(size_t)n * hidden + c]);
     out[(size_t)n * hidden + c] = from_f32<T>(acc);
   }
 }
@@ -693,7 +703,8 @@ Q25_EXPORT int q25_moe_combine_bf16(const float* y, const int* pr, const float* 
 
 template <typename T, int TOK>
 static int moe_route_softmax_shape(const void* h, const float* router, const float* correction, int* topk_idx, float* topk_w, int* counts,
-                                   int n_tokens, int hidden, int experts, int outputs, int top, int groups, int keep, cudaStream_t stream) {
+                                   int n_tokens, int hidden, int experts, int outputs, int top, int groups, int keep, int renorm,
+                                   float weight_scale, cudaStream_t stream) {
   const size_t smem = (size_t)TOK * (((hidden + 3) & ~3) + 3 * (MOE_MAX_EXPERTS + 1)) * sizeof(float);
   if (smem > 200 * 1024) return -1;
   if (smem > 48 * 1024) {
@@ -701,44 +712,45 @@ static int moe_route_softmax_shape(const void* h, const float* router, const flo
     if (e != cudaSuccess) return (int)e;
   }
   launch(moe_route_softmax_kernel<T, TOK>, dim3((n_tokens + TOK - 1) / TOK), dim3(256), smem, stream, (const T*)h, router, correction,
-         topk_idx, topk_w, counts, n_tokens, hidden, experts, outputs, top, groups, keep);
+         topk_idx, topk_w, counts, n_tokens, hidden, experts, outputs, top, groups, keep, renorm, weight_scale);
   return launch_status();
 }
 
 template <typename T>
 static int moe_route_softmax(const void* h, const float* router, const float* correction, int* topk_idx, float* topk_w, int* counts,
-                             int n_tokens, int hidden, int experts, int outputs, int top, int groups, int keep, void* stream) {
+                             int n_tokens, int hidden, int experts, int outputs, int top, int groups, int keep, int renorm,
+                             float weight_scale, void* stream) {
   if (n_tokens <= 0) return 0;
   if (experts <= 0 || outputs < experts || outputs > MOE_MAX_EXPERTS || top <= 0 || top > MOE_MAX_TOP || groups < 1 || outputs % groups ||
       keep < 1 || keep > groups || top > keep * (outputs / groups))
     return (int)cudaErrorInvalidValue;
   cudaStream_t s = (cudaStream_t)stream;
   int rc = -1;
-  if (n_tokens >= 512) rc = moe_route_softmax_shape<T, 4>(h, router, correction, topk_idx, topk_w, counts, n_tokens, hidden, experts, outputs, top, groups, keep, s);
-  if (rc == -1) rc = moe_route_softmax_shape<T, 1>(h, router, correction, topk_idx, topk_w, counts, n_tokens, hidden, experts, outputs, top, groups, keep, s);
+  if (n_tokens >= 512) rc = moe_route_softmax_shape<T, 4>(h, router, correction, topk_idx, topk_w, counts, n_tokens, hidden, experts, outputs, top, groups, keep, renorm, weight_scale, s);
+  if (rc == -1) rc = moe_route_softmax_shape<T, 1>(h, router, correction, topk_idx, topk_w, counts, n_tokens, hidden, experts, outputs, top, groups, keep, renorm, weight_scale, s);
   return rc == -1 ? (int)cudaErrorInvalidValue : rc;
 }
 Q25_EXPORT int q25_moe_route_softmax_f32(const void* h, const float* r, const float* corr, int* ti, float* tw, int* counts, int n, int hidden,
-                                         int experts, int outputs, int top, int groups, int keep, void* s) {
-  return moe_route_softmax<float>(h, r, corr, ti, tw, counts, n, hidden, experts, outputs, top, groups, keep, s);
+                                         int experts, int outputs, int top, int groups, int keep, int renorm, float wscale, void* s) {
+  return moe_route_softmax<float>(h, r, corr, ti, tw, counts, n, hidden, experts, outputs, top, groups, keep, renorm, wscale, s);
 }
 Q25_EXPORT int q25_moe_route_softmax_bf16(const void* h, const float* r, const float* corr, int* ti, float* tw, int* counts, int n, int hidden,
-                                          int experts, int outputs, int top, int groups, int keep, void* s) {
-  return moe_route_softmax<bf16>(h, r, corr, ti, tw, counts, n, hidden, experts, outputs, top, groups, keep, s);
+                                          int experts, int outputs, int top, int groups, int keep, int renorm, float wscale, void* s) {
+  return moe_route_softmax<bf16>(h, r, corr, ti, tw, counts, n, hidden, experts, outputs, top, groups, keep, renorm, wscale, s);
 }
 
 template <typename T>
-static int moe_combine_weighted(const float* y, const int* pair_row, const float* topk_w, const void* h, void* out, int n_tokens, int hidden,
-                                int top, void* stream) {
+static int moe_combine_weighted(const float* y, const int* pair_row, const float* topk_w, const void* h, const void* shared, void* out,
+                                int n_tokens, int hidden, int top, void* stream) {
   if (n_tokens <= 0) return 0;
   if (top > MOE_MAX_TOP) return (int)cudaErrorInvalidValue;
   launch(moe_combine_weighted_kernel<T>, dim3(n_tokens), dim3(hidden >= 2048 ? 256 : 128), 0, (cudaStream_t)stream, y, pair_row, topk_w,
-         (const T*)h, (T*)out, n_tokens, hidden, top);
+         (const T*)h, (const T*)shared, (T*)out, n_tokens, hidden, top);
   return launch_status();
 }
-Q25_EXPORT int q25_moe_combine_weighted_f32(const float* y, const int* pr, const float* tw, const void* h, void* out, int n, int hd, int top, void* s) {
-  return moe_combine_weighted<float>(y, pr, tw, h, out, n, hd, top, s);
+Q25_EXPORT int q25_moe_combine_weighted_f32(const float* y, const int* pr, const float* tw, const void* h, const void* sh, void* out, int n, int hd, int top, void* s) {
+  return moe_combine_weighted<float>(y, pr, tw, h, sh, out, n, hd, top, s);
 }
-Q25_EXPORT int q25_moe_combine_weighted_bf16(const float* y, const int* pr, const float* tw, const void* h, void* out, int n, int hd, int top, void* s) {
-  return moe_combine_weighted<bf16>(y, pr, tw, h, out, n, hd, top, s);
+Q25_EXPORT int q25_moe_combine_weighted_bf16(const float* y, const int* pr, const float* tw, const void* h, const void* sh, void* out, int n, int hd, int top, void* s) {
+  return moe_combine_weighted<bf16>(y, pr, tw, h, sh, out, n, hd, top, s);
 }

@@ -1,4 +1,4 @@
 """Model assembly and the architectures this engine knows.  Importing registers them."""
 
-from . import labolix, mozutar, qwen2_5_vl, rirulix  # noqa: F401
+from . import fatilix, labolix, mozutar, qwen2_5_vl, rirulix  # noqa: F401
 from .decoder import DecoderModel, StopRuntime  # noqa: F401

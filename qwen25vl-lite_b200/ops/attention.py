@@ -276,14 +276,16 @@ def plan_biased(host, group: int, window: int, keep_first: int) -> Dict[str, np.
 
 
 def attend_biased(ctx, plan, qkv, kv, nq: int, nkv: int, dk: int, dv: int, window, keep_first: int, scale: float,
-                  r1, r2, sink=None, v_row: int = 0, softcap: float = 0.0) -> torch.Tensor:
+                  r1, r2, sink=None, v_row: int = 0, softcap: float = 0.0, dist_bias=None, gate_off: int = -1) -> torch.Tensor:
     """qkv: [N, nq*dk (+ ...)] rows that begin with the queries, this step's keys and values already in
     the pages.  ``sink``: float32 [nq] joining each head's denominator; ``v_row``: the values lie inside
-    the key rows, that many channels apart; ``softcap`` c > 0: scaled scores become c * tanh(score / c).
+    the key rows, that many channels apart; ``softcap`` c > 0: scaled scores become c * tanh(score / c);
+    ``dist_bias``: float32 [rows, nq] added to the score by distance (the last row for every distance beyond);
+    ``gate_off`` >= 0: the rows of ``qkv`` hold nq * dv gate channels there, whose sigmoid multiplies the result.
     Returns [N, nq * dv]."""
     out = torch.empty((qkv.shape[0], nq * dv), dtype=qkv.dtype, device=qkv.device)
     window, keep_first = int(window or 0), int(keep_first or 0)
-    if kernels.biased_attention_mma_supports(qkv.dtype, dk, dv) and (v_row or dv) % 8 == 0:
+    if kernels.biased_attention_mma_supports(qkv.dtype, dk, dv) and (v_row or dv) % 8 == 0 and (gate_off < 0 or gate_off % 2 == 0):
         items, tiles = plan.get("decode_items"), _pairs(plan.get("tiles64"))
         splits, scratch = 1, None
         if items is not None:
@@ -292,9 +294,10 @@ def attend_biased(ctx, plan, qkv, kv, nq: int, nkv: int, dk: int, dv: int, windo
             if splits > 1:
                 scratch = _scratch_floats(items.shape[0] * nq * splits * (dv + 2), qkv.device, "biased")
         kernels.biased_attention_mma(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos, tiles, items,
-                                     nq, nkv, dk, dv, kv.page_size, window, keep_first, scale, r1, r2, splits, scratch, sink, v_row, softcap)
+                                     nq, nkv, dk, dv, kv.page_size, window, keep_first, scale, r1, r2, splits, scratch, sink, v_row, softcap,
+                                     dist_bias, gate_off)
         return out
     kernels.biased_attention_generic(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.token_seq, ctx.cu_q,
                                      ctx.q_start_pos, nq, nkv, dk, dv, kv.page_size, int(window or 0), int(keep_first or 0),
-                                     scale, r1, r2, sink, v_row, softcap)
+                                     scale, r1, r2, sink, v_row, softcap, dist_bias, gate_off)
     return out

@@ -26,13 +26,13 @@ _SIGNATURES = {
     "q25_silu_mul": [_P, _P, _I, _I, _I, _P],
     "q25_rope_store": [_P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "q25_paged_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
-    "q25_embed_position_norm": [_P, _P, _P, _P, _P, _F, _P, _I, _I, _I, _I, _I, _P],
+    "q25_embed_position_norm": [_P, _P, _P, _P, _P, _F, _P, _I, _I, _I, _I, _I, _F, _P],
     "q25_add_norm_groups": [_P, _P, _P, _F, _I, _P, _F, _I, _P, _P, _I, _I, _P],
     "q25_glu_clamped": [_P, _P, _I, _I, _F, _F, _F, _I, _P],
     "q25_rglru_conv": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "q25_rglru_scan": [_P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _I, _I, _P],
-    "q25_biased_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _I, _F, _P],
-    "q25_biased_attention_qk_norm_store": [_P, _I, _P, _P, _F, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "q25_biased_attention_generic": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _I, _F, _P, _I, _I, _P],
+    "q25_biased_attention_qk_norm_store": [_P, _I, _P, _P, _F, _I, _P, _I, _I, _P, _F, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "q25_add_dyt": [_P, _P, _P, _P, _F, _P, _P, _I, _I, _P],
     "q25_rotary_apply": [_P, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "q25_latent_store": [_P, _I, _I, _I, _P, _F, _P, _I, _I, _P, _P, _I, _P],
@@ -42,8 +42,9 @@ _SIGNATURES = {
     "q25_moe_gate_up": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _F, _I, _P, _P],
     "q25_moe_down": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "q25_moe_combine": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
-    "q25_moe_route_softmax": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
-    "q25_moe_combine_weighted": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "q25_moe_route_softmax": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],
+    "q25_moe_combine_weighted": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "q25_activation": [_P, _P, _LL, _I, _P],
     "q25_add_layernorm": [_P, _P, _P, _P, _P, _F, _P, _P, _F, _P, _P, _I, _I, _P],
     "q25_branch_mean_norm": [_P, _P, _I, _P, _I, _I, _F, _P],
     "q25_stream_pair": [_P, _P, _P, _I, _I, _P],
@@ -405,7 +406,7 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out
         _stream()), "gemm_f32")
 
 
-SKINNY_STORE, SKINNY_BIAS, SKINNY_F32, SKINNY_SWIGLU, SKINNY_RESIDUAL, SKINNY_GLU = 0, 1, 2, 3, 4, 5
+SKINNY_STORE, SKINNY_BIAS, SKINNY_F32, SKINNY_SWIGLU, SKINNY_RESIDUAL, SKINNY_GLU, SKINNY_RELU2 = 0, 1, 2, 3, 4, 5, 6
 # Rows the weight-streaming kernel takes: the 8 batch columns of one m16n8k16 MMA.  A variant with two
 # column tiles ran 9 to 16 rows; measured against the library path on B200 it lost at every size (a
 # decode step of 9 / 12 / 16 requests at the 3B sizes 2.64 / 2.66 / 2.65 ms against 2.43 / 2.55 / 2.59,
@@ -433,7 +434,8 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
     ``epilogue``: SKINNY_STORE, SKINNY_BIAS (float32 bias), SKINNY_F32 (float32 out),
     SKINNY_SWIGLU (w rows are groups of 8 gate + 8 up features; out has half as many columns),
     SKINNY_GLU (the same layout with the clamped gated unit; ``bias`` then holds its two constants,
-    float32 [limit, alpha]) or SKINNY_RESIDUAL (out is float32 and the product is added into it).  Runs as an operation
+    float32 [limit, alpha]), SKINNY_RELU2 (the square of relu of the product) or SKINNY_RESIDUAL (out is float32 and
+    the product is added into it).  Runs as an operation
     of the chain kernel (``csrc/gemm_chain.cu``): at once and alone, or, between ``chain_begin``
     and ``chain_end``, together with the products around it."""
     m, k = x.shape
@@ -645,23 +647,27 @@ def apply_penalties(logits: torch.Tensor, ids: torch.Tensor, counts: torch.Tenso
 
 
 def embed_position_norm(table: torch.Tensor, pos_table: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor,
-                        weight: torch.Tensor, eps: float, groups: int, x_out: torch.Tensor) -> None:
-    """x_out[n, :] (float32) = norm_in_groups(table[ids[n]] + pos_table[positions[n]]) * weight."""
+                        weight: Optional[torch.Tensor], eps: float, groups: int, x_out: torch.Tensor, scale: float = 1.0) -> None:
+    """x_out[n, :] (float32) = norm_in_groups(table[ids[n]] * scale + pos_table[positions[n]]) * weight; without a
+    weight there is no norm and the sum starts the stream as it is."""
     n, hidden = x_out.shape
     _dev(ids, torch.int32, "embed_position_norm ids"); _dev(positions, torch.int32, "embed_position_norm positions")
-    _dev(x_out, torch.float32, "embed_position_norm out"); _dev(weight, torch.float32, "embed_position_norm weight")
+    _dev(x_out, torch.float32, "embed_position_norm out")
+    if weight is not None:
+        _dev(weight, torch.float32, "embed_position_norm weight")
     if pos_table.dtype != table.dtype or hidden % groups:
         raise KernelError("embed_position_norm: the two tables share a dtype and the groups divide the width")
     _check(_typed("q25_embed_position_norm", table.dtype)(
-        table.data_ptr(), pos_table.data_ptr(), ids.data_ptr(), positions.data_ptr(), weight.data_ptr(), float(eps),
-        x_out.data_ptr(), n, hidden, table.shape[0], pos_table.shape[0], int(groups), _stream()), "embed_position_norm")
+        table.data_ptr(), pos_table.data_ptr(), ids.data_ptr(), positions.data_ptr(), _ptr(weight), float(eps),
+        x_out.data_ptr(), n, hidden, table.shape[0], pos_table.shape[0], int(groups), float(scale), _stream()), "embed_position_norm")
 
 
 def add_norm_groups(x: torch.Tensor, delta: Optional[torch.Tensor], delta_weight: Optional[torch.Tensor], delta_eps: float,
                     delta_groups: int, weight: Optional[torch.Tensor], eps: float, groups: int,
                     out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None, dtype: Optional[torch.dtype] = None) -> None:
     """x += d with d = delta, or norm_in_groups(delta) * delta_weight when a weight is given; then
-    out = norm_in_groups(x) * weight (out None: only the addition).  ``rows`` as for ``add_rmsnorm``."""
+    out = norm_in_groups(x) * weight (out None: only the addition; weight None: out = x as it is, in out's dtype).
+    ``rows`` as for ``add_rmsnorm``."""
     hidden = x.shape[-1]
     dtype = out.dtype if out is not None else (delta.dtype if delta is not None else dtype)
     n_out = out.shape[0] if out is not None else (rows.shape[0] if rows is not None else x.shape[0])
@@ -757,20 +763,30 @@ def biased_attention_generic(qkv: torch.Tensor, out: torch.Tensor, k_pages: torc
                              block_table: torch.Tensor, token_seq: torch.Tensor, cu_q: torch.Tensor, q_start_pos: torch.Tensor,
                              nq: int, nkv: int, dk: int, dv: int, page_size: int, window: int, keep_first: int, scale: float,
                              r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], sink: Optional[torch.Tensor] = None,
-                             v_row: int = 0, softcap: float = 0.0) -> None:
+                             v_row: int = 0, softcap: float = 0.0, dist_bias: Optional[torch.Tensor] = None, gate_off: int = -1) -> None:
     """``sink`` (float32 [nq]): a score per query head that has no key and no value and joins the
     softmax's denominator.  ``v_row``: channels between two value rows of a page when the values lie
     inside the key rows (0: the values have pages of their own, rows of ``dv`` channels).  ``softcap`` c > 0:
-    the scaled score becomes ``c * tanh(score / c)`` before anything else is added to it."""
+    the scaled score becomes ``c * tanh(score / c)`` before anything else is added to it.  ``dist_bias`` (float32
+    [rows, nq]): ``dist_bias[min(i - j, rows - 1), head]`` is added to the score.  ``gate_off`` >= 0: the rows of ``qkv``
+    hold nq * dv gate channels from that offset on, and the result is multiplied by their sigmoid."""
     if sink is not None:
         _dev(sink, torch.float32, "attention sink")
+    _check_dist_bias(dist_bias, nq)
     if dv > 512:
         raise KernelError(f"attention: value size {dv} is beyond 512")
     _check(_typed("q25_biased_attention_generic", qkv.dtype)(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], token_seq.data_ptr(), cu_q.data_ptr(), q_start_pos.data_ptr(), qkv.shape[0], nq, nkv, dk, dv,
         page_size, int(window or 0), int(keep_first or 0), float(scale), _ptr(r1), _ptr(r2), _ptr(sink), int(v_row or 0), float(softcap or 0.0),
-        _stream()), "biased_attention_generic")
+        _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], int(gate_off), _stream()), "biased_attention_generic")
+
+
+def _check_dist_bias(dist_bias: Optional[torch.Tensor], nq: int) -> None:
+    if dist_bias is not None:
+        _dev(dist_bias, torch.float32, "attention distance table")
+        if dist_bias.dim() != 2 or dist_bias.shape[1] != nq or dist_bias.shape[0] < 1 or not dist_bias.is_contiguous():
+            raise KernelError(f"attention: the distance table must be [rows, {nq}] float32, got {tuple(dist_bias.shape)}")
 
 
 # rows of a latent cache the tensor-core kernels are also built for: (rank + rotated channels, rank)
@@ -787,12 +803,13 @@ def biased_attention_mma(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
                          nq: int, nkv: int, dk: int, dv: int, page_size: int, window: int, keep_first: int, scale: float,
                          r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], n_splits: int = 1,
                          scratch: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None, v_row: int = 0,
-                         softcap: float = 0.0) -> None:
+                         softcap: float = 0.0, dist_bias: Optional[torch.Tensor] = None, gate_off: int = -1) -> None:
     """Tensor-core attention (bfloat16): ``tiles`` int32 [n, 2] are (entry, tile of 64 (token, head of
     the group) rows) of the runs, ``items`` the entries that bring one token, whose keys are cut into
     ``n_splits`` ranges (partial results through ``scratch``, float32, len(items) * nq * n_splits * (dv + 2))."""
     n_items = 0 if items is None else items.shape[0]
     n_tiles = 0 if tiles is None else tiles.shape[0]
+    _check_dist_bias(dist_bias, nq)
     part_o = part_ml = 0
     if n_items and n_splits > 1:
         need = n_items * nq * n_splits * (dv + 2)
@@ -803,11 +820,12 @@ def biased_attention_mma(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
     if not biased_attention_mma_supports(qkv.dtype, dk, dv) or (n_items and nq // nkv > 16):
         raise KernelError(f"biased_attention_mma: unsupported sizes {dk}/{dv} or more than 16 heads per kv head for single tokens")
     _check(_fn("q25_biased_attention_mma_bf16",
-               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _I, _I, _P, _P, _F, _P])(
+               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _I, _I, _P, _P, _F, _P, _I, _I, _P])(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], cu_q.data_ptr(), q_start_pos.data_ptr(), _ptr(tiles), n_tiles, _ptr(items), n_items, nq, nkv, dk, dv,
         page_size, int(window or 0), int(keep_first or 0), float(scale), _ptr(r1), _ptr(r2), _ptr(sink), int(v_row or 0), int(n_splits),
-        part_o, part_ml, float(softcap or 0.0), _stream()), "biased_attention_mma")
+        part_o, part_ml, float(softcap or 0.0), _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], int(gate_off),
+        _stream()), "biased_attention_mma")
     count_replayed((1 if n_tiles and n_items else 0) + (1 if n_items and n_splits > 1 else 0))
 
 
@@ -1023,11 +1041,12 @@ def moe_combine(y: torch.Tensor, pair_row: torch.Tensor, sg: Optional[torch.Tens
 
 
 def moe_route_softmax(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], experts: int, top: int, groups: int,
-                      keep: int, topk_idx: torch.Tensor, topk_w: torch.Tensor, counts: torch.Tensor) -> None:
+                      keep: int, topk_idx: torch.Tensor, topk_w: torch.Tensor, counts: torch.Tensor, renorm: bool = False,
+                      weight_scale: float = 1.0) -> None:
     """Router logits in float32 over all rows of ``router`` (the last ``rows - experts`` stand for experts without
     matrices), scores = softmax; the ``top`` largest of score + correction inside the ``keep`` best of ``groups``
-    equal runs of rows are chosen and weigh in with their plain scores; ``counts`` (one per expert with matrices)
-    takes how many tokens chose each."""
+    equal runs of rows are chosen and weigh in with their plain scores (``renorm``: divided by their sum + 1e-20), times
+    ``weight_scale``; ``counts`` (one per expert with matrices) takes how many tokens chose each."""
     n, hidden = h.shape
     outputs = router.shape[0]
     _dev(router, torch.float32, "moe_route_softmax router"); _dev(topk_idx, torch.int32, "moe_route_softmax idx")
@@ -1036,15 +1055,32 @@ def moe_route_softmax(h: torch.Tensor, router: torch.Tensor, correction: Optiona
         _dev(correction, torch.float32, "moe_route_softmax correction")
     _check(_typed("q25_moe_route_softmax", h.dtype)(h.data_ptr(), router.data_ptr(), _ptr(correction), topk_idx.data_ptr(), topk_w.data_ptr(),
                                                     counts.data_ptr(), n, hidden, int(experts), outputs, int(top), int(groups), int(keep),
-                                                    _stream()), "moe_route_softmax")
+                                                    int(bool(renorm)), float(weight_scale), _stream()), "moe_route_softmax")
 
 
-def moe_combine_weighted(y: torch.Tensor, pair_row: torch.Tensor, topk_w: torch.Tensor, h: torch.Tensor, out: torch.Tensor, top: int) -> None:
-    """out[n] = sum over the token's choices of weight * (the row of ``y`` the choice has, or h[n] itself when it has none)."""
+def moe_combine_weighted(y: torch.Tensor, pair_row: torch.Tensor, topk_w: torch.Tensor, h: torch.Tensor, out: torch.Tensor, top: int,
+                         shared: Optional[torch.Tensor] = None) -> None:
+    """out[n] = sum over the token's choices of weight * (the row of ``y`` the choice has, or h[n] itself when it has none),
+    plus ``shared[n]`` when given (the result of an expert that every token uses)."""
     n, hidden = out.shape
     _dev(y, torch.float32, "moe_combine_weighted rows"); _dev(h, out.dtype, "moe_combine_weighted input")
-    _check(_typed("q25_moe_combine_weighted", out.dtype)(y.data_ptr(), pair_row.data_ptr(), topk_w.data_ptr(), h.data_ptr(), out.data_ptr(),
-                                                         n, hidden, int(top), _stream()), "moe_combine_weighted")
+    if shared is not None:
+        _dev(shared, out.dtype, "moe_combine_weighted shared")
+        if shared.shape != out.shape or not shared.is_contiguous():
+            raise KernelError("moe_combine_weighted: the shared expert's result has the output's shape")
+    _check(_typed("q25_moe_combine_weighted", out.dtype)(y.data_ptr(), pair_row.data_ptr(), topk_w.data_ptr(), h.data_ptr(), _ptr(shared),
+                                                         out.data_ptr(), n, hidden, int(top), _stream()), "moe_combine_weighted")
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1}
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """out = act(x) element by element (``out`` may be ``x``): ``relu2`` the square of relu, ``gelu_tanh`` gelu in its
+    tanh form."""
+    if out.dtype != x.dtype or out.shape != x.shape or not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError("activation: input and output are contiguous tensors of one shape and dtype")
+    _check(_typed("q25_activation", x.dtype)(x.data_ptr(), out.data_ptr(), x.numel(), ACTIVATIONS[kind], _stream()), "activation")
 
 
 # ---- layer norm around the residual stream, branches into one update, a stream mixed with another ---------
@@ -1109,16 +1145,24 @@ def stream_set(x: torch.Tensor, y: torch.Tensor, bias: torch.Tensor) -> None:
 
 def qk_norm_store(qk: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                   angles: Optional[torch.Tensor], layout: str, k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
-                  kv_slot: Optional[torch.Tensor], nq: int, nkv: int, dk: int, page_size: int, keys_as_values: bool) -> None:
+                  kv_slot: Optional[torch.Tensor], nq: int, nkv: int, dk: int, page_size: int, keys_as_values: bool,
+                  unit_norm: bool = False, positions: Optional[torch.Tensor] = None, temp_coef: float = 0.0, temp_every: int = 0,
+                  dv: int = 0) -> None:
     """Rows [nq query heads | nkv key heads] of ``dk`` channels: every head divided by its root mean square and
-    multiplied by its weight (dk numbers, shared by the heads), then turned by ``angles``; queries are written back,
-    keys go to the pages at ``kv_slot``; with ``keys_as_values`` the keys as they came go to the value pages."""
+    multiplied by its weight (dk numbers, shared by the heads; without weights only divided when ``unit_norm``, else
+    left alone), then turned by ``angles``; queries are written back, keys go to the pages at ``kv_slot``; with
+    ``keys_as_values`` the keys as they came go to the value pages, with ``dv`` > 0 the nkv value heads of ``dv``
+    channels that follow the keys in a row.  ``temp_every`` > 0: the queries of a token at position p (``positions``,
+    int32 [N]) are multiplied by ``1 + temp_coef * ln(floor((p + 1) / temp_every) + 1)``."""
     half = 0 if angles is None else angles.shape[1]
     if qk.stride(1) != 1:
         raise KernelError("qk_norm_store: rows must be contiguous")
+    if temp_every:
+        _dev(positions, torch.int32, "qk_norm_store positions")
     _check(_typed("q25_biased_attention_qk_norm_store", qk.dtype)(
-        qk.data_ptr(), qk.stride(0), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(angles), half, ROTARY_LAYOUTS[layout], _ptr(k_pages),
-        _ptr(v_pages), _ptr(kv_slot), qk.shape[0], int(nq), int(nkv), int(dk), int(page_size), int(keys_as_values), _stream()), "qk_norm_store")
+        qk.data_ptr(), qk.stride(0), _ptr(q_weight), _ptr(k_weight), float(eps), int(bool(unit_norm)), _ptr(angles), half,
+        ROTARY_LAYOUTS[layout], _ptr(positions) if temp_every else 0, float(temp_coef), int(temp_every or 0), _ptr(k_pages), _ptr(v_pages),
+        _ptr(kv_slot), qk.shape[0], int(nq), int(nkv), int(dk), int(dv or 0), int(page_size), int(keys_as_values), _stream()), "qk_norm_store")
 
 
 # ---- matrix memories with gates that depend on the token -------------------------------------------------

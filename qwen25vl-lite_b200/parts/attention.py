@@ -169,6 +169,30 @@ class BiasedWindowAttention(Mixer):
         return self.o_proj(out)
 
 
+def log_distance_buckets(rows: int, far: float):
+    """Which row of a learned table of ``rows`` rows a distance n = 0, 1, 2, ... reads: the first half of the rows one
+    per distance, the second half spread over the distances up to ``far`` in equal steps of the logarithm, the last
+    row for every distance beyond:
+
+        bucket(n) = n                                                                   for n < rows / 2
+                  = min(rows - 1, rows / 2 + floor(ln(n / (rows / 2)) / ln(far / (rows / 2)) * (rows - rows / 2)))
+
+    Returns the buckets of the distances 0 .. L - 1, L - 1 being the first distance from which on the bucket is the
+    last row (every larger distance reads that row too)."""
+    import math
+
+    half = rows // 2
+    if rows < 2 or not far > half:
+        raise ValueError(f"a distance table of {rows} rows cannot spread its second half up to a distance of {far}")
+    out, n = [], 0
+    while True:
+        b = n if n < half else min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+        out.append(b)
+        if b == rows - 1 and n >= half:
+            return out
+        n += 1
+
+
 def _sink_tensor(sink, tensors, heads: int, device):
     """float32 [heads] for the kernels: the learned numbers, zeros for a sink whose score is 0, None for none."""
     if sink == "learned":
@@ -186,7 +210,17 @@ class SinkAttention(Mixer):
     has no key and no value; it is ``"learned"`` (one number per query head, the tensor ``sink``),
     ``"zero"`` (its score is 0: one is added to the denominator) or None.  The layer's position
     encoding (``position``, a ``rotary``) turns the first channels of every query and key head; values
-    are not turned.  Tensors: ``q``, ``k``, ``v``, ``o`` (and ``sink``).
+    are not turned; a position encoding that turns nothing (the model's positions enter elsewhere) is fine.
+    Tensors: ``q``, ``k``, ``v``, ``o`` (and ``sink``).
+
+    More options.  ``qkv_bias``: q, k and v have biases (``q.b``, ``k.b``, ``v.b``), added in the projection.
+    ``qk_norm_weight`` False: the query/key norm has no weights (heads are only divided by their root mean square).
+    ``q_temp`` = (coef, every): the queries of the token at position p are multiplied by
+    ``1 + coef * ln(floor((p + 1) / every) + 1)`` after their norm.  ``distance_bias`` = (rows, far): a learned table
+    ``rel`` [rows, heads] adds ``rel[bucket(i - j), h]`` to the scaled score (``log_distance_buckets``); the sink gets
+    none; rows None: as many as the checkpoint's tensor has.  ``out_gate``: the concatenated heads are multiplied channel by channel with ``sigmoid(Wg h)`` (tensor ``g``,
+    the same input as the projections) before ``o``; the gate's product rides with q, k, v and the sigmoid is the
+    attention kernels' epilogue.
 
     Three more options.  ``softcap`` c > 0: the scaled score becomes ``c * tanh(score / c)``.
     ``qk_norm_eps`` (a number): before the rotation every query and key head is divided by its root mean
@@ -200,9 +234,17 @@ class SinkAttention(Mixer):
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: Optional[int] = None,
                  scale: Optional[float] = None, window: Optional[int] = None, sink: Optional[str] = None, position=None,
-                 softcap: float = 0.0, qk_norm_eps: Optional[float] = None, values_from_keys: bool = False):
+                 softcap: float = 0.0, qk_norm_eps: Optional[float] = None, values_from_keys: bool = False, qkv_bias: bool = False,
+                 qk_norm_weight: bool = True, q_temp=None, distance_bias=None, out_gate: bool = False):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads cannot share {num_kv_heads} kv heads")
+        self.qkv_bias, self.qk_norm_weight, self.out_gate = bool(qkv_bias), bool(qk_norm_weight), bool(out_gate)
+        self.q_temp = None if not q_temp else (float(q_temp[0]), int(q_temp[1]))
+        if self.q_temp is not None and self.q_temp[1] < 1:
+            raise ValueError(f"the query temperature grows every {q_temp[1]} positions: at least 1")
+        self.distance_bias = None if not distance_bias else (int(distance_bias[0] or -1), float(distance_bias[1]))
+        if self.distance_bias is not None and self.distance_bias[0] > 0:
+            log_distance_buckets(*self.distance_bias)            # refuses sizes that do not go together
         if sink not in (None, "zero", "learned"):
             raise ValueError(f"sink is None, 'zero' or 'learned', got {sink!r}")
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
@@ -216,22 +258,39 @@ class SinkAttention(Mixer):
         self.window = None if not window else int(window)
         self.softcap = float(softcap or 0.0)
         self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
-        self.sink_kind, self.position = sink, position
-        if position is not None and position.dims > self.head_dim:
+        # an encoding that turns no channel (positions that enter at the embedding or as a bias) is none to this mixer
+        self.sink_kind, self.position = sink, position if getattr(position, "dims", 0) > 0 else None
+        if self.position is not None and position.dims > self.head_dim:
             raise ValueError(f"the position encoding turns {position.dims} channels, a head has {head_dim}")
-        self.qkv_proj = self.o_proj = self.sink = self.q_norm = self.k_norm = None
+        self.qkv_proj = self.o_proj = self.sink = self.q_norm = self.k_norm = self.dist_table = None
 
     @property
     def _fused_store(self) -> bool:
-        return self.values_from_keys or self.qk_norm_eps is not None
+        return self.values_from_keys or self.qk_norm_eps is not None or self.q_temp is not None
+
+    @property
+    def _gate_off(self) -> int:
+        """Where a projected row holds the gate channels: behind queries, keys and values (-1: no gate)."""
+        if not self.out_gate:
+            return -1
+        return (self.num_heads + self.num_kv_heads) * self.head_dim + (0 if self.values_from_keys else self.num_kv_heads * self.value_dim)
 
     def tensor_specs(self):
         h, q = self.hidden_size, self.num_heads * self.head_dim
-        specs = [TensorSpec("q", (q, h)), TensorSpec("k", (self.num_kv_heads * self.head_dim, h))]
+        k, v = self.num_kv_heads * self.head_dim, self.num_kv_heads * self.value_dim
+        specs = [TensorSpec("q", (q, h)), TensorSpec("k", (k, h))]
         if not self.values_from_keys:
-            specs.append(TensorSpec("v", (self.num_kv_heads * self.value_dim, h)))
-        if self.qk_norm_eps is not None:
+            specs.append(TensorSpec("v", (v, h)))
+        if self.qkv_bias:
+            specs += [TensorSpec("q.b", (q,), "bias"), TensorSpec("k.b", (k,), "bias")]
+            if not self.values_from_keys:
+                specs.append(TensorSpec("v.b", (v,), "bias"))
+        if self.qk_norm_eps is not None and self.qk_norm_weight:
             specs += [TensorSpec("q.norm", (self.head_dim,), "norm"), TensorSpec("k.norm", (self.head_dim,), "norm")]
+        if self.distance_bias is not None:
+            specs.append(TensorSpec("rel", (self.distance_bias[0], self.num_heads), "bias"))
+        if self.out_gate:
+            specs.append(TensorSpec("g", (self.num_heads * self.value_dim, h)))
         specs.append(TensorSpec("o", (h, self.num_heads * self.value_dim)))
         if self.sink_kind == "learned":
             specs.append(TensorSpec("sink", (self.num_heads,), "bias"))
@@ -241,13 +300,24 @@ class SinkAttention(Mixer):
         return KVCacheNeed(self.num_kv_heads, self.head_dim, self.window, self.value_dim)
 
     def load(self, tensors, device, dtype):
-        w = torch.cat([tensors["q"], tensors["k"]] + ([] if self.values_from_keys else [tensors["v"]]), dim=0)
-        self.qkv_proj = Linear(w.to(device=device, dtype=dtype).contiguous())
+        names = ["q", "k"] + ([] if self.values_from_keys else ["v"])
+        w = torch.cat([tensors[n] for n in names] + ([tensors["g"]] if self.out_gate else []), dim=0)
+        b = None
+        if self.qkv_bias:           # the gate has no bias: zeros ride behind those of q, k and v
+            b = torch.cat([tensors[n + ".b"].to(torch.float32) for n in names] +
+                          ([torch.zeros(self.num_heads * self.value_dim)] if self.out_gate else []), dim=0)
+            b = b.to(device=device, dtype=torch.float32).contiguous()
+        self.qkv_proj = Linear(w.to(device=device, dtype=dtype).contiguous(), b)
         self.o_proj = Linear(tensors["o"].to(device=device, dtype=dtype).contiguous())
         self.sink = _sink_tensor(self.sink_kind, tensors, self.num_heads, device)
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.qk_norm_weight:
             self.q_norm = tensors["q.norm"].to(device=device, dtype=torch.float32).contiguous()
             self.k_norm = tensors["k.norm"].to(device=device, dtype=torch.float32).contiguous()
+        if self.distance_bias is not None:
+            # the table by distance: row n is the learned row of n's bucket; the kernels read row min(i - j, rows - 1)
+            rel = tensors["rel"].to(device=device, dtype=torch.float32)
+            buckets = log_distance_buckets(rel.shape[0], self.distance_bias[1])
+            self.dist_table = rel[torch.tensor(buckets, dtype=torch.long, device=rel.device)].contiguous()
 
     def plan_key(self):
         return ("biased_window_attention", self.num_heads // self.num_kv_heads, self.window or 0, 0)
@@ -263,11 +333,11 @@ class SinkAttention(Mixer):
             angles = self.position.angles(ctx) if self.position is not None else None
             layout = self.position.layout if self.position is not None else "halves"
             own = stop.owns_cache
-            if own and not self.values_from_keys:      # values of their own: they go first, with keys that the next kernel replaces
-                kernels.kv_store_mix(qkv, None, 0.0, kv.k_pages, kv.v_pages, kv.kv_slot, nq, nkv, dk, dv, kv.page_size)
+            coef, every = self.q_temp or (0.0, 0)
             kernels.qk_norm_store(qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, angles, layout, kv.k_pages if own else None,
                                   kv.v_pages if own else None, kv.kv_slot if own else None, nq, nkv, dk, kv.page_size,
-                                  self.values_from_keys)
+                                  self.values_from_keys, unit_norm=self.qk_norm_eps is not None, positions=ctx.positions[0],
+                                  temp_coef=coef, temp_every=every, dv=0 if self.values_from_keys else dv)
         else:
             if self.position is not None:
                 qk = qkv[:, :(nq + nkv) * dk].unflatten(1, (nq + nkv, dk))       # query heads, then key heads
@@ -275,7 +345,7 @@ class SinkAttention(Mixer):
             if stop.owns_cache:
                 kernels.kv_store_mix(qkv, None, 0.0, kv.k_pages, kv.v_pages, kv.kv_slot, nq, nkv, dk, dv, kv.page_size)
         out = attention_ops.attend_biased(ctx, ctx.plan(self), qkv, kv, nq, nkv, dk, dv, self.window, 0, self.scale, None, None,
-                                          self.sink, softcap=self.softcap)
+                                          self.sink, softcap=self.softcap, dist_bias=self.dist_table, gate_off=self._gate_off)
         return self.o_proj(out, residual=residual)
 
 

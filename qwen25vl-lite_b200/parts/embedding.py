@@ -40,30 +40,34 @@ class TokenEmbedding(Part):
 
 @register_embedding("learned_position_embedding")
 class LearnedPositionEmbedding(Part):
-    """``x = norm(E[token] + P[position])``: a token table, a learned vector per position (added as it
-    is), and a norm (in ``norm_groups`` groups) whose result starts the residual stream.  One kernel.
-    The tensors' names in a checkpoint are parameters."""
+    """``x = norm(E[token] * scale + P[position])``: a token table whose rows are multiplied by ``scale``, a learned
+    vector per position (added as it is), and a norm (in ``norm_groups`` groups) whose result starts the residual
+    stream.  One kernel.  The tensors' names in a checkpoint are parameters; a norm name of None means that there is
+    no norm and the sum starts the stream as it is."""
 
     graph_safe = True                # forward is a fixed sequence of this engine's kernels
 
-    def __init__(self, vocab_size: int, hidden_size: int, max_positions: int, norm_eps: float, norm_groups: int = 1,
-                 names=("weight", "positions", "norm")):
+    def __init__(self, vocab_size: int, hidden_size: int, max_positions: int, norm_eps: float = 0.0, norm_groups: int = 1,
+                 names=("weight", "positions", "norm"), scale: float = 1.0):
         self.vocab_size, self.hidden_size, self.max_positions = int(vocab_size), int(hidden_size), int(max_positions)
-        self.norm_eps, self.norm_groups = float(norm_eps), int(norm_groups)
+        self.norm_eps, self.norm_groups, self.scale = float(norm_eps), int(norm_groups), float(scale)
         if self.norm_groups < 1 or self.hidden_size % self.norm_groups:
             raise ValueError(f"a norm over {hidden_size} channels cannot be cut into {norm_groups} equal groups")
         self.token_name, self.position_name, self.norm_name = names
         self.weight = self.positions = self.norm_weight = None
 
     def tensor_specs(self):
-        return (TensorSpec(self.token_name, (self.vocab_size, self.hidden_size)),
-                TensorSpec(self.position_name, (self.max_positions, self.hidden_size)),
-                TensorSpec(self.norm_name, (self.hidden_size,), init="norm"))
+        specs = [TensorSpec(self.token_name, (self.vocab_size, self.hidden_size)),
+                 TensorSpec(self.position_name, (self.max_positions, self.hidden_size))]
+        if self.norm_name is not None:
+            specs.append(TensorSpec(self.norm_name, (self.hidden_size,), init="norm"))
+        return tuple(specs)
 
     def load(self, tensors, device, dtype):
         self.weight = tensors[self.token_name].to(device=device, dtype=dtype).contiguous()
         self.positions = tensors[self.position_name].to(device=device, dtype=dtype).contiguous()
-        self.norm_weight = tensors[self.norm_name].to(device=device, dtype=torch.float32).contiguous()
+        if self.norm_name is not None:
+            self.norm_weight = tensors[self.norm_name].to(device=device, dtype=torch.float32).contiguous()
 
     def exports(self):
         return {self.token_name: self.weight}
@@ -71,7 +75,7 @@ class LearnedPositionEmbedding(Part):
     def forward(self, ctx):
         x = torch.empty((ctx.n_tokens, self.hidden_size), dtype=torch.float32, device=self.weight.device)
         kernels.embed_position_norm(self.weight, self.positions, ctx.token_ids, ctx.positions[0], self.norm_weight,
-                                    self.norm_eps, self.norm_groups, x)
+                                    self.norm_eps, self.norm_groups, x, self.scale)
         return x
 
 

@@ -63,6 +63,47 @@ class SwiGLU(FeedForward):
         return self.down_proj(act, residual=residual)
 
 
+@register_feed_forward("activated_mlp")
+class ActivatedMLP(FeedForward):
+    """A dense feed-forward without a gate and without biases: ``Wd act(Wu h)``.  ``activation``: ``"relu2"``, the
+    square of relu ``max(z, 0)^2``, or ``"gelu_tanh"``, ``0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))``.
+    In bfloat16 the square of relu is the up product's epilogue: in the weight-streaming kernel for steps of up to
+    8 rows, in the tcgen05 product for long steps; everywhere else a kernel of its own follows the product."""
+
+    graph_safe = True                # forward is a fixed sequence of this engine's kernels
+    accepts_residual = True          # the down projection can add into the residual stream itself
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "relu2", names=("up", "down")):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        if activation not in kernels.ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}; known: {sorted(kernels.ACTIVATIONS)}")
+        self.activation = activation
+        self.up_name, self.down_name = names
+        self.up_proj = self.down_proj = None
+
+    def tensor_specs(self):
+        h, i = self.hidden_size, self.intermediate_size
+        return (TensorSpec(self.up_name, (i, h)), TensorSpec(self.down_name, (h, i)))
+
+    def load(self, tensors, device, dtype):
+        self.up_proj = Linear(tensors[self.up_name].to(device=device, dtype=dtype).contiguous())
+        self.down_proj = Linear(tensors[self.down_name].to(device=device, dtype=dtype).contiguous())
+
+    def forward(self, ctx, h, residual=None):
+        w = self.up_proj.weight
+        fused = self.activation == "relu2"
+        if fused and kernels.gemm_skinny_supports(h, w):
+            act = torch.empty((h.shape[0], self.intermediate_size), dtype=ctx.dtype, device=h.device)
+            kernels.gemm_skinny(h, w, None, act, kernels.SKINNY_RELU2)
+        elif fused and linear.use_tcgen05(h, w, fused_epilogue=True):
+            act = torch.empty((h.shape[0], self.intermediate_size), dtype=ctx.dtype, device=h.device)
+            kernels.gemm_tcgen05(h, w, None, act, kernels.SKINNY_RELU2)
+        else:
+            act = self.up_proj(h)
+            kernels.activation(act, act, self.activation)
+        return self.down_proj(act, residual=residual)
+
+
 TCGEN05_MIN_WIDTH = 2048        # from this width on the grouped products of long steps run on tcgen05
 
 
@@ -192,8 +233,10 @@ class GroupedRoutedGLU(FeedForward):
     The choice looks at ``s + correction`` (a learned vector); the outputs form ``groups`` equal runs of neighbours,
     a run's mark is its largest such number, and only outputs of the ``keep`` runs with the largest marks can be
     chosen (the others count as minus infinity).  The ``top`` largest are chosen and weigh in with their plain scores
-    ``s``, not renormalised; the weight multiplies the expert's *output*.  The last ``identity`` outputs stand for
-    experts without tensors whose output is their input.  Tensors: ``router``, ``correction``, ``e<i>.gate|up|down``.
+    ``s``: as they are, or with ``renorm`` divided by their sum (+ 1e-20); either way times ``weight_scale``.  The weight
+    multiplies the expert's *output*.  The last ``identity`` outputs stand for experts without tensors whose output is
+    their input.  ``shared_size``: one more expert of the same form and that size (``shared.gate|up|down``) that every
+    token uses, added unweighted.  Tensors: ``router``, ``correction``, ``e<i>.gate|up|down``.
 
     The choice, the sort by expert and the grouped products are those of ``routed_glu`` (``csrc/moe.cu``); a choice of
     an identity expert takes no row of the products and is added by the kernel that sums a token's choices."""
@@ -201,10 +244,14 @@ class GroupedRoutedGLU(FeedForward):
     graph_safe = True                # forward is a fixed sequence of this engine's kernels
 
     def __init__(self, hidden_size: int, experts: int, top: int, expert_size: int, identity: int = 0, groups: int = 1, keep: int = 1,
-                 correction: bool = True):
+                 correction: bool = True, renorm: bool = False, weight_scale: float = 1.0, shared_size: Optional[int] = None):
         self.hidden_size, self.experts, self.top, self.expert_size = int(hidden_size), int(experts), int(top), int(expert_size)
         self.identity, self.groups, self.keep = int(identity), max(int(groups), 1), max(int(keep), 1)
         self.has_correction = bool(correction)
+        self.renorm, self.weight_scale = bool(renorm), float(weight_scale)
+        self.shared = None
+        if shared_size:
+            self.shared = SwiGLU(self.hidden_size, int(shared_size), names=("shared.gate", "shared.up", "shared.down"))
         outputs = self.experts + self.identity
         if self.experts < 1 or self.identity < 0 or outputs > 256 or not 1 <= self.top <= 16:
             raise ValueError(f"the router takes up to 256 outputs and chooses 1 to 16 of them, got {outputs} and {top}")
@@ -221,7 +268,12 @@ class GroupedRoutedGLU(FeedForward):
         specs.append(TensorSpec("router", (self.experts + self.identity, h), "matrix_wide"))
         if self.has_correction:
             specs.append(TensorSpec("correction", (self.experts + self.identity,), "bias"))
+        if self.shared is not None:
+            specs += list(self.shared.tensor_specs())
         return tuple(specs)
+
+    def sub_parts(self):
+        return () if self.shared is None else (self.shared,)
 
     def load(self, tensors, device, dtype):
         self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0)
@@ -229,13 +281,16 @@ class GroupedRoutedGLU(FeedForward):
         self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(self.experts)]).to(device=device, dtype=dtype).contiguous()
         self.router = tensors["router"].to(device=device, dtype=torch.float32).contiguous()
         self.correction = tensors["correction"].to(device=device, dtype=torch.float32).contiguous() if self.has_correction else None
+        if self.shared is not None:
+            self.shared.load(tensors, device, dtype)
 
     def forward(self, ctx, h):
+        shared = None if self.shared is None else self.shared.forward(ctx, h)
         route = lambda idx, w, counts: kernels.moe_route_softmax(h, self.router, self.correction, self.experts, self.top, self.groups,
-                                                                 self.keep, idx, w, counts)
+                                                                 self.keep, idx, w, counts, self.renorm, self.weight_scale)
         y, pair_row, topk_w = _run_experts(ctx, h, self.w_gate_up, self.w_down, self.top, route, False, float("inf"), 1.0, 0.0)
         out = torch.empty((h.shape[0], self.hidden_size), dtype=ctx.dtype, device=h.device)
-        kernels.moe_combine_weighted(y, pair_row, topk_w, h, out, self.top)
+        kernels.moe_combine_weighted(y, pair_row, topk_w, h, out, self.top, shared)
         return out
 
 

@@ -1,4 +1,4 @@
-"""Normalisations fused with the residual update: RMS norm, Dynamic Tanh, layer norm.
+"""Normalisations fused with the residual update: RMS norm, Dynamic Tanh, layer norm, and no norm at all.
 
 Formula (reference src/qwen25vl_lite/layers.py:27-31): ``x * rsqrt(mean(x^2) + eps) * w``,
 statistics in float32, plain (not 1 + w) weight.  With ``groups`` > 1 the vector is cut into
@@ -19,13 +19,18 @@ from .base import Norm, PendingUpdate, TensorSpec, register_norm
 class RMSNorm(Norm):
     graph_safe = True                # forward is a fixed sequence of this engine's kernels
 
-    def __init__(self, dim: int, eps: float, groups: int = 1, name: str = "weight", optional: bool = False):
+    def __init__(self, dim: int, eps: float, groups: int = 1, name: str = "weight", optional: bool = False, offset: float = 0.0,
+                 gain: float = 1.0):
         """``name``: what the weight is called in a checkpoint, after the part's prefix.
         ``optional``: a norm that its block does not run (a layer without the sublayer it belongs
-        to); a checkpoint may hold its weight or not."""
+        to); a checkpoint may hold its weight or not.
+        ``offset``: the norm multiplies by ``offset + w``, w being what the checkpoint holds (1: a weight kept as its distance from one).
+        ``gain``: a constant that multiplies the norm's result (a block that adds ``m * norm(update)`` into the
+        stream); both are folded into the float32 weight when the part is loaded."""
         self.dim = int(dim)
         self.eps = float(eps)
         self.groups = int(groups)
+        self.offset, self.gain = float(offset), float(gain)
         if self.groups < 1 or self.dim % self.groups:
             raise ValueError(f"a norm over {self.dim} channels cannot be cut into {groups} equal groups")
         self.name = name
@@ -37,9 +42,18 @@ class RMSNorm(Norm):
 
     def load(self, tensors, device, dtype):
         if self.name in tensors:
-            self.weight = tensors[self.name].to(device=device, dtype=torch.float32).contiguous()
+            w = tensors[self.name].to(device=device, dtype=torch.float32)
+            if self.offset != 0.0:
+                w = w + self.offset
+            if self.gain != 1.0:
+                w = w * self.gain
+            self.weight = w.contiguous()
         elif not self.optional:
             raise KeyError(self.name)
+
+    def add_only(self, ctx, x, value):
+        """x += norm(value) with this norm, and nothing else: for a pending update that no norm follows."""
+        kernels.add_norm_groups(x, value, self.weight, self.eps, self.groups, None, 0.0, 1, None, None, dtype=ctx.dtype)
 
     def forward(self, ctx, x, delta, rows=None, defer=False):
         """``defer``: the caller's consumer can normalise inside its own kernel; when nothing
@@ -62,6 +76,30 @@ class RMSNorm(Norm):
                 raise TypeError("a pending update can be normalised by an rmsnorm only")
             kernels.add_norm_groups(x, delta, None if post is None else post.weight, 0.0 if post is None else post.eps,
                                     1 if post is None else post.groups, self.weight, self.eps, self.groups, out, rows)
+        return out
+
+
+@register_norm("stream_cast")
+class StreamCast(Norm):
+    """No norm: the sublayer reads the residual stream itself.  What is left of a norm's work is the addition of the
+    pending update (normalised by its own RMS norm on its way in, when it is a ``PendingUpdate``) and the stream's
+    rounding to the activation dtype, in the one kernel that the other norms use for both.  It has no tensors."""
+
+    graph_safe = True                # forward is a fixed sequence of this engine's kernels
+
+    def __init__(self, dim: int):
+        self.dim = int(dim)
+
+    def forward(self, ctx, x, delta, rows=None, defer=False):
+        post = None
+        if isinstance(delta, PendingUpdate):
+            post, delta = delta.norm, delta.value
+            if not isinstance(post, RMSNorm):
+                raise TypeError("a pending update can be normalised by an rmsnorm only")
+        n_out = x.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((n_out, self.dim), dtype=ctx.dtype, device=x.device)
+        kernels.add_norm_groups(x, delta, None if post is None else post.weight, 0.0 if post is None else post.eps,
+                                1 if post is None else post.groups, None, 0.0, 1, out, rows)
         return out
 
 
