@@ -110,7 +110,7 @@ def _mlp(mlp: Optional[Dict[str, Any]], where: str):
     shared = mlp.get("shared")
     return FatilixRoutedFf(experts=experts, top=top, ff=int(_need(_need(mlp, "expert", where), "ff", where + ".expert")), groups=count,
                            keep=keep, scale=float(r.get("scale", 1.0)),
-                           shared_ff=int(_need(shared, "ff", where + ".shared")) if shared else None)
+                           shared_ff=int(_need(shared, "ff", where + ".shared")) if shared is not None else None)
 
 
 @dataclass(frozen=True)

@@ -38,7 +38,8 @@ class RMSNorm(Norm):
         self.weight = None
 
     def tensor_specs(self):
-        return (TensorSpec(self.name, (self.dim,), init="norm", optional=self.optional),)
+        # a weight that the norm adds its offset to is drawn around zero, a plain one around one
+        return (TensorSpec(self.name, (self.dim,), init="norm" if self.offset == 0.0 else "bias", optional=self.optional),)
 
     def load(self, tensors, device, dtype):
         if self.name in tensors:
