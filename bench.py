@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the engine at Qwen2.5-VL sizes, random bfloat16 weights.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 3b|7b-trace|32b|rirulix|labolix|mozutar]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 3b|7b-trace|32b|rirulix|labolix|mozutar|fatilix]
 
 One "step" is one decode step of the whole batch.  The default run (``--config 3b``) has the 3B
 layer sizes: the headline ``value`` is decoded tokens a second at batch 8 after 2,048-token
@@ -11,7 +11,7 @@ out every step).  The same line carries the 2,048-token prefill, the decode step
 decode at batch 1 and 64, the clocks seen while timing, and the number of this engine's kernel
 launches in the timed region.  ``--config 7b-trace`` runs a continuous-batching trace of 128
 requests at the 7B sizes, ``--config 32b`` decode at batch 1 / 8 / 32 after 8,192-token prompts and
-a 2,048-token prefill at the 32B sizes, ``--config rirulix`` / ``--config labolix`` / ``--config mozutar`` prefill and decode of the Rirulix / Labolix / Mozutar design
+a 2,048-token prefill at the 32B sizes, ``--config rirulix`` / ``--config labolix`` / ``--config mozutar`` / ``--config fatilix`` prefill and decode of the Rirulix / Labolix / Mozutar / Fatilix design
 at a few layer sizes beside this decoder at equal size; each prints one line of its own.
 The engine is single-GPU: for --gpus N > 1 one line says so and the exit code is 2.
 """
@@ -535,6 +535,31 @@ MOZUTAR_SIZES = {
 }
 
 
+def _fatilix_sizes(width, layers, heads, kv_heads, dim, experts, groups, keep, top, ff, shared_ff, dense_ff, vocab):
+    """A Fatilix model of ``layers`` layers (attention with a distance table and a dense squared-relu feed-forward, then
+    attention whose values are its keys with routed experts and a shared one, and so on) and the Qwen2.5-VL text decoder
+    of equal size beside it: the same width, layers, heads and vocabulary, a feed-forward as wide as the dense one."""
+    temp = {"coef": 0.1, "every": 512}
+    table = {"type": "attention_2", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5 * 1.5,
+                                              "q_temp": temp, "bias_max": 128, "bias_rows": 32},
+             "mlp": {"kind": "dense", "ff": dense_ff}}
+    keys = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5 * 1.5, "q_temp": temp},
+            "mlp": {"kind": "moe", "expert": {"ff": ff}, "shared": {"ff": shared_ff},
+                    "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": groups, "keep": keep}}}}
+    ours = {"architecture": "Fatilix", "vocab": vocab, "width": width, "max_positions": 8192, "norm": {"eps": 1e-6},
+            "embedding": {"scale": float(width) ** 0.5}, "residual_mult": 0.7, "layers": [(table, keys)[i % 2] for i in range(layers)]}
+    closest = _sizes(width, layers, heads, kv_heads, dense_ff, vocab, False)
+    closest["text_config"]["rope_scaling"]["mrope_section"] = [dim // 8, 3 * dim // 16, 3 * dim // 16]
+    return ours, closest
+
+
+FATILIX_SIZES = {
+    "w1024": _fatilix_sizes(1024, 6, 8, 2, 128, 8, 4, 2, 2, 1408, 1408, 2816, 32000),
+    "w2048": _fatilix_sizes(2048, 6, 16, 2, 128, 16, 4, 2, 2, 2816, 2816, 5632, 32000),
+    "w2560_d64": _fatilix_sizes(2560, 6, 40, 8, 64, 32, 8, 4, 4, 1728, 1728, 6912, 32000),
+}
+
+
 def run_rirulix(args):
     """Prefill and decode throughput of the Rirulix design at a few layer sizes, each beside the
     Qwen2.5-VL text decoder of equal size, random weights: a 2,048-token prompt in one step, and
@@ -551,6 +576,11 @@ def run_labolix(args):
 def run_mozutar(args):
     """The same measurement for the Mozutar design."""
     return _run_design(args, "Mozutar", "mozutar", MOZUTAR_SIZES)
+
+
+def run_fatilix(args):
+    """The same measurement for the Fatilix design."""
+    return _run_design(args, "Fatilix", "fatilix", FATILIX_SIZES)
 
 
 def _run_design(args, design, label_ours, all_sizes):
@@ -609,9 +639,9 @@ def main(argv=None):
     ap.add_argument("--only-batch", type=int, default=0, help="time decode steps at this batch size only (for profilers)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
                     help="float32 times the true 32-bit path of the 3b configuration (fewer --layers advised)")
-    ap.add_argument("--only-size", default="", help="with --config rirulix, labolix or mozutar: one of its sizes only (for profilers)")
-    ap.add_argument("--config", default="3b", choices=["3b", "7b-trace", "32b", "rirulix", "labolix", "mozutar"],
-                    help="3b: the headline line (default); 7b-trace, 32b: the other workloads, one line each; rirulix, labolix, mozutar: "
+    ap.add_argument("--only-size", default="", help="with --config rirulix, labolix, mozutar or fatilix: one of its sizes only (for profilers)")
+    ap.add_argument("--config", default="3b", choices=["3b", "7b-trace", "32b", "rirulix", "labolix", "mozutar", "fatilix"],
+                    help="3b: the headline line (default); 7b-trace, 32b: the other workloads, one line each; rirulix, labolix, mozutar, fatilix: "
                          "that design at a few layer sizes beside the Qwen2.5-VL decoder of equal size")
     args = ap.parse_args(argv)
     if args.gpus != 1:
@@ -624,7 +654,7 @@ def main(argv=None):
             print(json.dumps({"impl": "reference", "unavailable": "the reference arm measures the 3b configuration only"}))
             return 0
         return run_reference(args)
-    return {"3b": run_ours, "7b-trace": run_7b_trace, "32b": run_32b, "rirulix": run_rirulix, "labolix": run_labolix, "mozutar": run_mozutar}[args.config](args)
+    return {"3b": run_ours, "7b-trace": run_7b_trace, "32b": run_32b, "rirulix": run_rirulix, "labolix": run_labolix, "mozutar": run_mozutar, "fatilix": run_fatilix}[args.config](args)
 
 
 if __name__ == "__main__":

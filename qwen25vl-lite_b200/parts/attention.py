@@ -304,9 +304,10 @@ class SinkAttention(Mixer):
         w = torch.cat([tensors[n] for n in names] + ([tensors["g"]] if self.out_gate else []), dim=0)
         b = None
         if self.qkv_bias:           # the gate has no bias: zeros ride behind those of q, k and v
-            b = torch.cat([tensors[n + ".b"].to(torch.float32) for n in names] +
-                          ([torch.zeros(self.num_heads * self.value_dim)] if self.out_gate else []), dim=0)
-            b = b.to(device=device, dtype=torch.float32).contiguous()
+            b = [tensors[n + ".b"].to(device=device, dtype=torch.float32) for n in names]
+            if self.out_gate:
+                b.append(torch.zeros(self.num_heads * self.value_dim, dtype=torch.float32, device=device))
+            b = torch.cat(b, dim=0).contiguous()
         self.qkv_proj = Linear(w.to(device=device, dtype=dtype).contiguous(), b)
         self.o_proj = Linear(tensors["o"].to(device=device, dtype=dtype).contiguous())
         self.sink = _sink_tensor(self.sink_kind, tensors, self.num_heads, device)

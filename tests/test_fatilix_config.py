@@ -167,3 +167,24 @@ def test_random_model_folder_and_plain_forward(tmp_path, name):
     other = plain.forward(config, w, ids[:25] + [(ids[25] + 1) % config["vocab"]] + ids[26:])
     np.testing.assert_allclose(other[:25], logits[:25], rtol=0, atol=1e-9)
     assert np.abs(other[25:] - logits[25:]).max() > 1e-3
+
+
+def test_command_line_writes_a_random_model_of_the_design(tmp_path):
+    """``random-model`` resolves the design through the registry; without rows in the file the distance table gets the
+    size random weights take for a size the checkpoint decides, and the folder loads into the plain model."""
+    import json
+
+    from qwen25vl_lite import cli
+    from qwen25vl_lite.parts.base import FREE_SIZE
+
+    raw = copy.deepcopy(F1)
+    del raw["layers"][0]["mixer"]["bias_rows"]
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(raw))
+    out = tmp_path / "model"
+    assert cli.main(["random-model", "--config", str(cfg), "--out", str(out), "--seed", "4"]) == 0
+    assert json.loads((out / "config.json").read_text())["architecture"] == "Fatilix"
+    config, w = plain.load_model_dir(str(out))
+    assert w["l0.mix.rel"].shape == (FREE_SIZE, 4)
+    assert np.abs(w["l0.norm1"]).max() < 0.2                     # weights that the norm adds one to are drawn around zero
+    assert np.isfinite(plain.forward_logits(config, w, [1, 2, 3])).all()
