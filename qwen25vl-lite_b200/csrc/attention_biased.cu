@@ -203,7 +203,8 @@ Q25_EXPORT int q25_kv_store_mix_bf16(void* qkv, int qs, const void* vo, int ldo,
   return kv_store_mix<bf16>(qkv, qs, vo, ldo, mix, kp, vp, slot, n, nq, nkv, dk, dv, ps, s);
 }
 
-// Queries and keys unit-normed per head and turned, keys kept as values: one block per token, a warp per head.
+// Queries and keys unit-normed per head and turned, keys kept as values: a warp per head, the heads of a token dealt to
+// gridDim.y blocks of four warps, so that every head has a warp of its own.
 // Row of the token: [nq query heads | nkv key heads] of dk channels each (| nkv value heads of dv channels).  Every
 // head is divided by its root mean square (eps inside the root) and multiplied by wq / wk (dk numbers shared by the
 // heads); without weights the heads are left as projected, or with unit_norm only divided.  Its first 2 * half
@@ -228,7 +229,7 @@ __global__ void qk_norm_store_kernel(T* __restrict__ qk, int qk_stride, const fl
   const int page = slot / page_size, in_page = slot % page_size;
   const float* ang = half > 0 ? angles + (size_t)n * half * 2 : nullptr;
   const float temper = temp_every > 0 ? 1.0f + temp_coef * logf((float)((positions[n] + 1) / temp_every) + 1.0f) : 1.0f;
-  for (int head = warp; head < nq + nkv; head += n_warps) {
+  for (int head = blockIdx.y * n_warps + warp; head < nq + nkv; head += gridDim.y * n_warps) {
     T* row = qk + (size_t)n * qk_stride + (size_t)head * dk;
     const bool is_key = head >= nq;
     const float* w = is_key ? wk : wq;
@@ -255,8 +256,91 @@ __global__ void qk_norm_store_kernel(T* __restrict__ qk, int qk_stride, const fl
   }
   if (dv > 0 && !keys_as_values && slot >= 0) {
     const T* vrow = qk + (size_t)n * qk_stride + (size_t)(nq + nkv) * dk;
-    for (int c = threadIdx.x; c < nkv * dv; c += blockDim.x)
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < nkv * dv; c += gridDim.y * blockDim.x)
       vpages[(((size_t)page * nkv + c / dv) * page_size + in_page) * dv + c % dv] = vrow[c];
+  }
+}
+
+// Four neighbouring channels as they lie in memory, and as floats.
+template <typename T> struct Raw4;
+template <> struct Raw4<float> { typedef float4 type; };
+template <> struct Raw4<bf16> { typedef uint2 type; };
+__device__ __forceinline__ float4 raw4_f32(const float4& r) { return r; }
+__device__ __forceinline__ float4 raw4_f32(const uint2& r) {
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void f32_raw4(const float4& v, float4& r) { r = v; }
+__device__ __forceinline__ void f32_raw4(const float4& v, uint2& r) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  r.x = *reinterpret_cast<const unsigned*>(&a);
+  r.y = *reinterpret_cast<const unsigned*>(&b);
+}
+
+#define QK_FLAT_CHUNKS 4          // a lane holds up to this many runs of four channels: heads of up to 512 channels
+
+// The same for heads that nothing turns, whose size is a multiple of four (and every row 16 bytes aligned): a warp per
+// (token, head), the head's channels in registers, four neighbouring channels a load and a store.  The value heads of a
+// row count as heads of their own that are only copied to their page.
+template <typename T>
+__global__ void qk_norm_store_flat_kernel(T* __restrict__ qk, int qk_stride, const float* __restrict__ wq, const float* __restrict__ wk,
+                                          float eps, int unit_norm, const int* __restrict__ positions, float temp_coef, int temp_every,
+                                          T* __restrict__ kpages, T* __restrict__ vpages, const int* __restrict__ kv_slot, int n_tokens,
+                                          int nq, int nkv, int dk, int dv, int page_size, int keys_as_values) {
+  pdl_trigger();
+  pdl_wait();
+  typedef typename Raw4<T>::type R4;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = nq + nkv + (dv > 0 && !keys_as_values ? nkv : 0);
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (item >= (long long)n_tokens * heads) return;
+  const int n = (int)(item / heads), head = (int)(item % heads);
+  const int slot = kv_slot ? kv_slot[n] : -1;
+  const int page = slot / page_size, in_page = slot % page_size;
+  if (head >= nq + nkv) {                                   // a value head: the row's own values to their page
+    if (slot < 0) return;
+    const int vh = head - nq - nkv;
+    const T* src = qk + (size_t)n * qk_stride + (size_t)(nq + nkv) * dk + (size_t)vh * dv;
+    T* dst = vpages + (((size_t)page * nkv + vh) * page_size + in_page) * dv;
+    if (dv % 4 == 0) {
+      for (int c = lane * 4; c < dv; c += 128) *reinterpret_cast<R4*>(dst + c) = *reinterpret_cast<const R4*>(src + c);
+    } else {
+      for (int c = lane; c < dv; c += 32) dst[c] = src[c];
+    }
+    return;
+  }
+  T* row = qk + (size_t)n * qk_stride + (size_t)head * dk;
+  const bool is_key = head >= nq;
+  const float* w = is_key ? wk : wq;
+  const size_t page_row = is_key ? ((size_t)page * nkv + (head - nq)) * page_size + in_page : 0;
+  float4 v[QK_FLAT_CHUNKS];
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < QK_FLAT_CHUNKS; ++i) {
+    const int c = lane * 4 + 128 * i;
+    if (c < dk) {
+      const R4 raw = *reinterpret_cast<const R4*>(row + c);
+      if (is_key && keys_as_values && slot >= 0) *reinterpret_cast<R4*>(vpages + page_row * dk + c) = raw;
+      v[i] = raw4_f32(raw);
+      sq = fmaf(v[i].x, v[i].x, sq); sq = fmaf(v[i].y, v[i].y, sq); sq = fmaf(v[i].z, v[i].z, sq); sq = fmaf(v[i].w, v[i].w, sq);
+    }
+  }
+  sq = warp_sum(sq);
+  float factor = (w || unit_norm) ? 1.0f / sqrtf(sq / (float)dk + eps) : 1.0f;
+  const float temper = !is_key && temp_every > 0 ? 1.0f + temp_coef * logf((float)((positions[n] + 1) / temp_every) + 1.0f) : 1.0f;
+  if (is_key && slot < 0) return;
+#pragma unroll
+  for (int i = 0; i < QK_FLAT_CHUNKS; ++i) {
+    const int c = lane * 4 + 128 * i;
+    if (c < dk) {
+      float4 x = make_float4(v[i].x * factor, v[i].y * factor, v[i].z * factor, v[i].w * factor);
+      if (w) { const float4 ww = *reinterpret_cast<const float4*>(w + c); x.x *= ww.x; x.y *= ww.y; x.z *= ww.z; x.w *= ww.w; }
+      if (!is_key) { x.x *= temper; x.y *= temper; x.z *= temper; x.w *= temper; }
+      R4 raw;
+      f32_raw4(x, raw);
+      *reinterpret_cast<R4*>(is_key ? kpages + page_row * dk + c : row + c) = raw;
+    }
   }
 }
 
@@ -269,7 +353,18 @@ static int qk_norm_store(void* qk, int qk_stride, const float* wq, const float* 
       temp_every < 0 || (temp_every > 0 && !positions) || dv < 0)
     return (int)cudaErrorInvalidValue;
   const int warps = 4;
-  launch(qk_norm_store_kernel<T>, dim3(n_tokens), dim3(warps * 32), (size_t)warps * dk * sizeof(float), (cudaStream_t)stream, (T*)qk,
+  const int chunk = 4;                                      // channels of a vector access
+  const bool aligned = !(((uintptr_t)qk | (uintptr_t)kpages | (uintptr_t)vpages) & (4 * sizeof(T) - 1)) && !(((uintptr_t)wq | (uintptr_t)wk) & 15);
+  if (half == 0 && dk % chunk == 0 && dk <= 128 * QK_FLAT_CHUNKS && qk_stride % chunk == 0 && aligned && (keys_as_values || dv % chunk == 0)) {
+    const long long heads = nq + nkv + (dv > 0 && !keys_as_values ? nkv : 0);
+    const unsigned blocks = (unsigned)(((long long)n_tokens * heads + 7) / 8);
+    launch(qk_norm_store_flat_kernel<T>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)qk, qk_stride, wq, wk, eps, unit_norm, positions,
+           temp_coef, temp_every, (T*)kpages, (T*)vpages, kv_slot, n_tokens, nq, nkv, dk, dv, page_size, keys_as_values);
+    return launch_status();
+  }
+  // as many blocks a token as its heads fill: a warp that walks several heads one after the other waits for each one's loads
+  const int per_token = (nq + nkv + warps - 1) / warps;
+  launch(qk_norm_store_kernel<T>, dim3(n_tokens, per_token), dim3(warps * 32), (size_t)warps * dk * sizeof(float), (cudaStream_t)stream, (T*)qk,
          qk_stride, wq, wk, eps, unit_norm, angles, half, layout, positions, temp_coef, temp_every, (T*)kpages, (T*)vpages, kv_slot, nq,
          nkv, dk, dv, page_size, keys_as_values);
   return launch_status();
@@ -388,7 +483,9 @@ __device__ __forceinline__ void biased_load_tile(unsigned char* ks, unsigned cha
 // One tile of keys for the warp's 16 rows.  p0/p1: positions of rows g and g+8 (-1: no such row);
 // b1x/b2x: the bias numbers of the rows' heads; [rl, rh]: the keys of the tile that count.  FULL: the
 // caller has seen that every key of the tile counts for every row of the warp, so nothing is masked.
-template <int DK, int DV, int BN, bool FULL>
+// TABLE: the rows' heads add tab0 / tab1 [min(distance, dist_rows - 1) * nq] to their scores (a build of
+// its own, so that the kernels without a table carry none of it).
+template <int DK, int DV, int BN, bool FULL, bool TABLE>
 __device__ __forceinline__ void biased_tile(const unsigned (&qf)[DK / 16][4], const unsigned char* ks, const unsigned char* vs,
                                             int key0, int rl, int rh, int p0, int p1, int window, int keep_first, float scale_log2,
                                             float cap_log2, float scale_over_cap, float b10, float b20, float b11, float b21,
@@ -414,7 +511,7 @@ __device__ __forceinline__ void biased_tile(const unsigned (&qf)[DK / 16][4], co
   // to all its scores; the table's entries are natural-log scores, the kernel's live in the base-2 domain
   constexpr float LOG2E = 1.4426950408889634f;
   const int last_row = dist_rows - 1;
-  const bool far0 = tab0 && p0 - (key0 + BN - 1) >= last_row, far1 = tab0 && p1 - (key0 + BN - 1) >= last_row;
+  const bool far0 = TABLE && p0 - (key0 + BN - 1) >= last_row, far1 = TABLE && p1 - (key0 + BN - 1) >= last_row;
   const float fb0 = far0 ? tab0[(size_t)last_row * nq] * LOG2E : 0.f, fb1 = far1 ? tab1[(size_t)last_row * nq] * LOG2E : 0.f;
   float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -425,7 +522,7 @@ __device__ __forceinline__ void biased_tile(const unsigned (&qf)[DK / 16][4], co
       const float b1 = e < 2 ? b10 : b11, b2 = e < 2 ? b20 : b21;
       float v = cap_log2 > 0.f ? cap_log2 * tanhf(s[j][e] * scale_over_cap) - b1 * __log2f(fmaf(b2, fd, 1.0f))
                                : fmaf(s[j][e], scale_log2, -b1 * __log2f(fmaf(b2, fd, 1.0f)));
-      if (tab0) {
+      if (TABLE) {
         if (e < 2 ? far0 : far1) {
           v += e < 2 ? fb0 : fb1;
         } else {
@@ -496,8 +593,11 @@ __device__ __forceinline__ bool tile_is_full(int key0, int bn, int rl, int rh, i
   return p_min >= 0 && last <= p_min && key0 >= rl && last <= rh && (window <= 0 || p_max - key0 < window || last < keep_first);
 }
 
-template <int DK, int DV>
+// EXTRA: what a build carries beyond scores, masks and sinks: 0 nothing, 1 the output gate, 2 the gate and the distance
+// table (kernels of models that have neither are built without a trace of them).
+template <int DK, int DV, int EXTRA>
 __global__ void __launch_bounds__(128) biased_prefill_kernel(BiasedArgs a) {
+  constexpr bool TABLE = EXTRA == 2, GATE = EXTRA >= 1;
   pdl_trigger();
   pdl_wait();
   constexpr int BN = 64, KT = BN * Tile<DK>::PITCH, VT = BN * Tile<DV>::PITCH;
@@ -519,8 +619,8 @@ __global__ void __launch_bounds__(128) biased_prefill_kernel(BiasedArgs a) {
   const int h0 = kvh * group + (r0 < rows ? r0 % group : 0), h1 = kvh * group + (r1 < rows ? r1 % group : 0);
   const int p0 = tok0 < 0 ? -1 : start + tok0, p1 = tok1 < 0 ? -1 : start + tok1;
   const float b10 = a.r1 ? a.r1[h0] : 0.f, b20 = a.r1 ? a.r2[h0] : 0.f, b11 = a.r1 ? a.r1[h1] : 0.f, b21 = a.r1 ? a.r2[h1] : 0.f;
-  const float* tab0 = a.dist_bias ? a.dist_bias + h0 : nullptr;
-  const float* tab1 = a.dist_bias ? a.dist_bias + h1 : nullptr;
+  const float* tab0 = TABLE ? a.dist_bias + h0 : nullptr;
+  const float* tab1 = TABLE ? a.dist_bias + h1 : nullptr;
   unsigned qf[DK / 16][4];
   load_q<DK>(qf, [&](int r) -> const bf16* {
     const int rr = tile_row0 + warp * 16 + r;
@@ -553,9 +653,9 @@ __global__ void __launch_bounds__(128) biased_prefill_kernel(BiasedArgs a) {
     __syncthreads();
     walk.tile(i, BN, key0, rl, rh);
     if (tile_is_full(key0, BN, rl, rh, wp_min, wp_max, a.window, a.keep_first))
-      biased_tile<DK, DV, BN, true>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, a.cap_log2, a.scale_over_cap, b10, b20, b11, b21, tab0, tab1, a.dist_rows, a.nq, m, l, o);
+      biased_tile<DK, DV, BN, true, TABLE>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, a.cap_log2, a.scale_over_cap, b10, b20, b11, b21, tab0, tab1, a.dist_rows, a.nq, m, l, o);
     else
-      biased_tile<DK, DV, BN, false>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, a.cap_log2, a.scale_over_cap, b10, b20, b11, b21, tab0, tab1, a.dist_rows, a.nq, m, l, o);
+      biased_tile<DK, DV, BN, false, TABLE>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, a.cap_log2, a.scale_over_cap, b10, b20, b11, b21, tab0, tab1, a.dist_rows, a.nq, m, l, o);
     __syncthreads();
   }
   float l0 = quad_sum(l[0]), l1 = quad_sum(l[1]);
@@ -564,22 +664,25 @@ __global__ void __launch_bounds__(128) biased_prefill_kernel(BiasedArgs a) {
     if (tok1 >= 0) l1 += exp2f(a.sink[h1] * 1.4426950408889634f - m[1]);
   }
   const float i0 = l0 > 0.f ? 1.0f / l0 : 0.f, i1 = l1 > 0.f ? 1.0f / l1 : 0.f;
-  const bf16* g0 = a.gate_off >= 0 && tok0 >= 0 ? a.qkv + (size_t)(first + tok0) * a.qkv_stride + a.gate_off + (size_t)h0 * DV : nullptr;
-  const bf16* g1 = a.gate_off >= 0 && tok1 >= 0 ? a.qkv + (size_t)(first + tok1) * a.qkv_stride + a.gate_off + (size_t)h1 * DV : nullptr;
+  const bf16* g0 = GATE && a.gate_off >= 0 && tok0 >= 0 ? a.qkv + (size_t)(first + tok0) * a.qkv_stride + a.gate_off + (size_t)h0 * DV : nullptr;
+  const bf16* g1 = GATE && a.gate_off >= 0 && tok1 >= 0 ? a.qkv + (size_t)(first + tok1) * a.qkv_stride + a.gate_off + (size_t)h1 * DV : nullptr;
 #pragma unroll
   for (int nb = 0; nb < DV / 8; ++nb) {
     const int c = nb * 8 + 2 * t;
     float y0 = o[nb][0] * i0, y1 = o[nb][1] * i0, y2 = o[nb][2] * i1, y3 = o[nb][3] * i1;
-    if (g0) { const float2 z = gate_pair(g0 + c); y0 *= z.x; y1 *= z.y; }
-    if (g1) { const float2 z = gate_pair(g1 + c); y2 *= z.x; y3 *= z.y; }
+    if (GATE) {
+      if (g0) { const float2 z = gate_pair(g0 + c); y0 *= z.x; y1 *= z.y; }
+      if (g1) { const float2 z = gate_pair(g1 + c); y2 *= z.x; y3 *= z.y; }
+    }
     if (tok0 >= 0) *reinterpret_cast<unsigned*>(a.out + (size_t)(first + tok0) * a.nq * DV + (size_t)h0 * DV + c) = pack_bf16(y0, y1);
     if (tok1 >= 0) *reinterpret_cast<unsigned*>(a.out + (size_t)(first + tok1) * a.nq * DV + (size_t)h1 * DV + c) = pack_bf16(y2, y3);
   }
 }
 
 // Single tokens: blockIdx.x = item, blockIdx.y = kv head, blockIdx.z = key range.
-template <int DK, int DV>
+template <int DK, int DV, int EXTRA>
 __global__ void __launch_bounds__(128) biased_decode_kernel(BiasedArgs a) {
+  constexpr bool TABLE = EXTRA == 2, GATE = EXTRA >= 1;
   pdl_trigger();
   pdl_wait();
   constexpr int BN = 32, KT = BN * Tile<DK>::PITCH, VT = BN * Tile<DV>::PITCH, WARP_BYTES = 2 * (KT + VT);
@@ -598,8 +701,8 @@ __global__ void __launch_bounds__(128) biased_decode_kernel(BiasedArgs a) {
   const int h0 = kvh * group + (g < group ? g : 0), h1 = kvh * group + (g + 8 < group ? g + 8 : 0);
   const int p0 = g < group ? p : -1, p1 = g + 8 < group ? p : -1;
   const float b10 = a.r1 ? a.r1[h0] : 0.f, b20 = a.r1 ? a.r2[h0] : 0.f, b11 = a.r1 ? a.r1[h1] : 0.f, b21 = a.r1 ? a.r2[h1] : 0.f;
-  const float* tab0 = a.dist_bias ? a.dist_bias + h0 : nullptr;
-  const float* tab1 = a.dist_bias ? a.dist_bias + h1 : nullptr;
+  const float* tab0 = TABLE ? a.dist_bias + h0 : nullptr;
+  const float* tab1 = TABLE ? a.dist_bias + h1 : nullptr;
   unsigned qf[DK / 16][4];
   load_q<DK>(qf, [&](int r) -> const bf16* {
     return r < group ? a.qkv + (size_t)token * a.qkv_stride + (size_t)(kvh * group + r) * DK : nullptr;
@@ -630,7 +733,7 @@ __global__ void __launch_bounds__(128) biased_decode_kernel(BiasedArgs a) {
     }
     __syncwarp();
     walk.tile(i, BN, key0, rl, rh);
-    biased_tile<DK, DV, BN, false>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, a.cap_log2, a.scale_over_cap, b10, b20, b11, b21, tab0, tab1, a.dist_rows, a.nq, m, l, o);
+    biased_tile<DK, DV, BN, false, TABLE>(qf, cur, cur + KT, key0, rl, rh, p0, p1, a.window, a.keep_first, a.scale_log2, a.cap_log2, a.scale_over_cap, b10, b20, b11, b21, tab0, tab1, a.dist_rows, a.nq, m, l, o);
     __syncwarp();
   }
   cp_async_wait<0>();
@@ -667,7 +770,7 @@ __global__ void __launch_bounds__(128) biased_decode_kernel(BiasedArgs a) {
     if (a.n_splits == 1) {
       if (a.sink && mm != -INFINITY) sum += exp2f(a.sink[head] * 1.4426950408889634f - mm);
       float y = sum > 0.f ? acc / sum : 0.f;
-      if (a.gate_off >= 0) y *= gate_one(a.qkv + (size_t)token * a.qkv_stride + a.gate_off + (size_t)head * DV + c);
+      if (GATE && a.gate_off >= 0) y *= gate_one(a.qkv + (size_t)token * a.qkv_stride + a.gate_off + (size_t)head * DV + c);
       a.out[(size_t)token * a.nq * DV + (size_t)head * DV + c] = __float2bfloat16_rn(y);
     } else {
       const size_t at = ((size_t)item * a.nq + head) * a.n_splits + split;
@@ -700,28 +803,28 @@ __global__ void biased_combine_kernel(BiasedArgs a) {
   a.out[(size_t)token * a.nq * DV + (size_t)head * DV + c] = __float2bfloat16_rn(y);
 }
 
-template <int DK, int DV>
+template <int DK, int DV, int EXTRA>
 static int biased_mma_launch(const BiasedArgs& a, int n_tiles, int n_items, const int* tiles, const int* items, cudaStream_t s) {
   if (n_tiles > 0) {
     constexpr int SMEM = 2 * 64 * (Tile<DK>::PITCH + Tile<DV>::PITCH);
     if (SMEM > 48 * 1024) {
-      const cudaError_t e = cudaFuncSetAttribute(biased_prefill_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+      const cudaError_t e = cudaFuncSetAttribute(biased_prefill_kernel<DK, DV, EXTRA>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
       if (e != cudaSuccess) return (int)e;
     }
     BiasedArgs b = a;
     b.items = tiles;
-    launch(biased_prefill_kernel<DK, DV>, dim3(n_tiles, a.nkv), dim3(128), SMEM, s, b);
+    launch(biased_prefill_kernel<DK, DV, EXTRA>, dim3(n_tiles, a.nkv), dim3(128), SMEM, s, b);
   }
   if (n_items > 0) {
     constexpr int TILES = 4 * 2 * 32 * (Tile<DK>::PITCH + Tile<DV>::PITCH), MERGE = (4 * 16 * 2 + 4 * 16 * (DV + 4)) * 4;
     constexpr int SMEM = TILES > MERGE ? TILES : MERGE;
     if (SMEM > 48 * 1024) {
-      const cudaError_t e = cudaFuncSetAttribute(biased_decode_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+      const cudaError_t e = cudaFuncSetAttribute(biased_decode_kernel<DK, DV, EXTRA>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
       if (e != cudaSuccess) return (int)e;
     }
     BiasedArgs b = a;
     b.items = items;
-    launch(biased_decode_kernel<DK, DV>, dim3(n_items, a.nkv, a.n_splits), dim3(128), SMEM, s, b);
+    launch(biased_decode_kernel<DK, DV, EXTRA>, dim3(n_items, a.nkv, a.n_splits), dim3(128), SMEM, s, b);
     if (a.n_splits > 1) launch(biased_combine_kernel<DV>, dim3(n_items, a.nq), dim3(DV), 0, s, b);
   }
   return launch_status();
@@ -761,7 +864,10 @@ Q25_EXPORT int q25_biased_attention_mma_bf16(const void* qkv, int qkv_stride, vo
   a.r1 = r1; a.r2 = r2; a.sink = sink; a.v_row = v_row > 0 ? v_row : dv; a.n_splits = n_splits; a.part_o = part_o; a.part_ml = part_ml;
   a.dist_bias = dist_bias; a.dist_rows = dist_bias ? dist_rows : 1; a.gate_off = gate_off;
   cudaStream_t s = (cudaStream_t)stream;
-#define BIASED_CASE(K, V) if (dk == K && dv == V) return biased_mma_launch<K, V>(a, n_tiles, n_items, tiles, items, s);
+#define BIASED_CASE(K, V) \
+  if (dk == K && dv == V) return dist_bias ? biased_mma_launch<K, V, 2>(a, n_tiles, n_items, tiles, items, s) \
+                                 : gate_off >= 0 ? biased_mma_launch<K, V, 1>(a, n_tiles, n_items, tiles, items, s) \
+                                                 : biased_mma_launch<K, V, 0>(a, n_tiles, n_items, tiles, items, s);
   BIASED_SIZES(BIASED_CASE)
 #undef BIASED_CASE
   return (int)cudaErrorInvalidValue;

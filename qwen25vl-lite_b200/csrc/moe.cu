@@ -166,7 +166,7 @@ moe_route_softmax_kernel(const T* __restrict__ h, const float* __restrict__ rout
       // fewer choosable rows than `top` (the host refuses such sizes): the choice is row 0 with weight 0
       const bool none = arg == 0x7fffffff;
       topk_idx[(size_t)n * top + k] = none ? 0 : arg;
-      topk_w[(size_t)n * top + k] = none ? 0.f : score[arg];
+      mark[k] = none ? 0.f : score[arg];                        // the marks of the runs have served: the chosen scores wait here
       if (!none) {
         choice[arg] = -INFINITY;
         if (arg < experts) atomicAdd(&counts[arg], 1);
@@ -176,12 +176,9 @@ moe_route_softmax_kernel(const T* __restrict__ h, const float* __restrict__ rout
     }
     __syncwarp();
   }
-  if (lane == 0 && (renorm || weight_scale != 1.0f)) {         // the lane that wrote the weights: in the order of the choices
-    float* w = topk_w + (size_t)n * top;
-    float sum = 0.f;
-    for (int k = 0; k < top; ++k) sum += w[k];
-    for (int k = 0; k < top; ++k) w[k] = (renorm ? w[k] / (sum + 1e-20f) : w[k]) * weight_scale;
-  }
+  float chosen = 0.f;                                           // in the order of the choices, the same in every lane
+  if (renorm) for (int k = 0; k < top; ++k) chosen += mark[k];
+  for (int k = lane; k < top; k += 32) topk_w[(size_t)n * top + k] = (renorm ? mark[k] / (chosen + 1e-20f) : mark[k]) * weight_scale;
 }
 
 // One block: where every expert's rows begin (each expert filled up to whole tiles of `tile` rows),
