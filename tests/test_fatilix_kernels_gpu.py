@@ -206,7 +206,7 @@ def distinct_table(rows, far, nq, seed):
 
 
 # (query heads, kv heads, key size, value size): sizes of the tensor-core kernels and others
-SHAPES = [(8, 4, 64, 64), (4, 2, 32, 64), (4, 1, 128, 128), (3, 1, 24, 20), (5, 5, 12, 12), (2, 2, 64, 32)]
+SHAPES = [(8, 4, 64, 64), (4, 2, 32, 64), (4, 1, 128, 128), (3, 1, 24, 20), (5, 5, 12, 12), (2, 2, 64, 32), (2, 1, 96, 64)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
