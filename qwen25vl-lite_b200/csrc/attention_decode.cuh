@@ -25,6 +25,11 @@ struct AttnArgs {
   int n_splits;
   float* part_o;      // [items, nq, splits, D]
   float* part_ml;     // [items, nq, splits, 2]
+  // what only the tcgen05 prefill kernel reads: a score per query head that has no key and no value and joins the
+  // softmax's denominator (nullptr: none), and where a token's row holds its nq * D output-gate channels, whose sigmoid
+  // multiplies the result (-1: no gate)
+  const float* sink;
+  int gate_off;
 };
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -678,5 +683,6 @@ static int fill_args(AttnArgs& a, const void* qkv, int qkv_stride, void* out, co
   a.vpages = (const bf16*)vp; a.block_table = bt; a.table_width = tw; a.cu_q = cu_q; a.q_start_pos = q_start;
   a.items = items; a.nq = nq; a.nkv = nkv; a.page_shift = shift; a.window = window;
   a.scale_log2 = scale * 1.4426950408889634f; a.n_splits = 1; a.part_o = nullptr; a.part_ml = nullptr;
+  a.sink = nullptr; a.gate_off = -1;
   return 0;
 }

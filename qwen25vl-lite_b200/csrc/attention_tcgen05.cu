@@ -2,7 +2,9 @@
 //
 // Same formula and masking as the other attention kernels (reference src/qwen25vl_lite/text.py:78,
 // 156-175, src/qwen25vl_lite/attention.py:143-148): S = Q K^T * D^-1/2, a query at position a sees
-// keys j <= a (and j > a - window), softmax over the keys in float, O = P V.
+// keys j <= a (and j > a - window), softmax over the keys in float, O = P V.  Two things more for models that have
+// them, both where a row's sums become its result: a sink per query head (a score without key or value that joins
+// the denominator) and an output gate (the result times the sigmoid of the row's gate channels).
 //
 // A CTA takes 128 rows = (token, query head of one kv group) pairs of one entry, so one pass over a
 // kv head's keys serves the whole group, and walks the keys in tiles of 64.  Its threads have two
@@ -118,6 +120,25 @@ struct A5Bars {
                                   // two phases away from its barrier, where a parity wait would be wrong
   unsigned tmem;
 };
+
+// The weight of a head's sink against the maximum the row's sums were taken with (both in the units of the exponent).
+__device__ __forceinline__ float a5_sink_weight(const AttnArgs& a, int head, float m) {
+  return a.sink && m != -INFINITY ? exp2f(a.sink[head] * 1.4426950408889634f - m) : 0.f;
+}
+// 32 neighbouring output channels times the sigmoid of their gate channels (16-byte aligned).
+__device__ __forceinline__ void a5_gate32(float (&v)[32], const bf16* g) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(g + q * 8);
+    const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 z = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+      v[q * 8 + 2 * i] *= 1.0f / (1.0f + __expf(-z.x));
+      v[q * 8 + 2 * i + 1] *= 1.0f / (1.0f + __expf(-z.y));
+    }
+  }
+}
 
 __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kernel(AttnArgs a, int n_sms, int* __restrict__ err) {
   constexpr int NROW = A5_NROW, ROWS = A5_ROWS;         // one thread per row; the warp after them issues the products
@@ -447,10 +468,11 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
       asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];\n" : "=f"(m1), "=f"(l1) : "r"(peer_ml + tid * 8) : "memory");
       const float M = fmaxf(m_used, m1);
       const float w0 = m_used == -INFINITY ? 0.f : a5_ex2(m_used - M), w1 = m1 == -INFINITY ? 0.f : a5_ex2(m1 - M);
-      const float L = l * w0 + l1 * w1;
+      const float L = l * w0 + l1 * w1 + (live ? a5_sink_weight(a, kvh * G + head, M) : 0.f);
       const float inv = live && L > 0.f ? 1.0f / L : 0.f;
       const float s0 = w0 * inv, s1 = w1 * inv;
       bf16* dst = a.out + (size_t)(q0 + tok) * a.nq * A5_D + (size_t)(kvh * G + head) * A5_D;
+      const bf16* gate = a.gate_off >= 0 && live ? a.qkv + (size_t)(q0 + tok) * a.qkv_stride + a.gate_off + (size_t)(kvh * G + head) * A5_D : nullptr;
 #pragma unroll
       for (int c = 0; c < A5_D / 32; ++c) {
         float mine[32], theirs[32];
@@ -463,6 +485,7 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
         if (!live) continue;
 #pragma unroll
         for (int j = 0; j < 32; ++j) mine[j] = mine[j] * s0 + theirs[j] * s1;
+        if (gate) a5_gate32(mine, gate + c * 32);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           uint4 o;
@@ -492,20 +515,25 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
       }
       if (live) *reinterpret_cast<float2*>(a.part_ml + slot * 2) = make_float2(m_used, l);
     } else {
-    const float inv = live && l > 0.f ? 1.0f / l : 0.f;
+    const float l_all = l + (live ? a5_sink_weight(a, kvh * G + head, m_used) : 0.f);
+    const float inv = live && l_all > 0.f ? 1.0f / l_all : 0.f;
     bf16* dst = a.out + (size_t)(q0 + tok) * a.nq * A5_D + (size_t)(kvh * G + head) * A5_D;
+    const bf16* gate = a.gate_off >= 0 && live ? a.qkv + (size_t)(q0 + tok) * a.qkv_stride + a.gate_off + (size_t)(kvh * G + head) * A5_D : nullptr;
 #pragma unroll
     for (int c = 0; c < A5_D / 32; ++c) {                 // tcgen05.ld is warp-wide: dead rows read too, and store nothing
       float part[32];
       tc5_ld32(t_o + c * 32, part);
       if (!live) continue;
 #pragma unroll
+      for (int j = 0; j < 32; ++j) part[j] *= inv;
+      if (gate) a5_gate32(part, gate + c * 32);
+#pragma unroll
       for (int q = 0; q < 4; ++q) {
         uint4 o;
-        o.x = pack_bf16(part[q * 8] * inv, part[q * 8 + 1] * inv);
-        o.y = pack_bf16(part[q * 8 + 2] * inv, part[q * 8 + 3] * inv);
-        o.z = pack_bf16(part[q * 8 + 4] * inv, part[q * 8 + 5] * inv);
-        o.w = pack_bf16(part[q * 8 + 6] * inv, part[q * 8 + 7] * inv);
+        o.x = pack_bf16(part[q * 8], part[q * 8 + 1]);
+        o.y = pack_bf16(part[q * 8 + 2], part[q * 8 + 3]);
+        o.z = pack_bf16(part[q * 8 + 4], part[q * 8 + 5]);
+        o.w = pack_bf16(part[q * 8 + 6], part[q * 8 + 7]);
         *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = o;
       }
     }
@@ -565,10 +593,18 @@ __global__ void __launch_bounds__(A5_MERGE_WARPS * 32, 4) attention_prefill_merg
       }
     }
   }
+  L += a5_sink_weight(a, kvh * G + head, M);
   const float inv = L > 0.f ? 1.0f / L : 0.f;
+  acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+  if (a.gate_off >= 0) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(a.qkv + (size_t)(q0 + tok) * a.qkv_stride + a.gate_off + (size_t)(kvh * G + head) * A5_D + lane * 4);
+    const float2 z0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x)), z1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    acc.x *= 1.0f / (1.0f + __expf(-z0.x)); acc.y *= 1.0f / (1.0f + __expf(-z0.y));
+    acc.z *= 1.0f / (1.0f + __expf(-z1.x)); acc.w *= 1.0f / (1.0f + __expf(-z1.y));
+  }
   uint2 packed;
-  packed.x = pack_bf16(acc.x * inv, acc.y * inv);
-  packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+  packed.x = pack_bf16(acc.x, acc.y);
+  packed.y = pack_bf16(acc.z, acc.w);
   *reinterpret_cast<uint2*>(a.out + (size_t)(q0 + tok) * a.nq * A5_D + (size_t)(kvh * G + head) * A5_D + lane * 4) = packed;
 }
 
@@ -583,9 +619,10 @@ Q25_EXPORT int q25_attention_prefill_tcgen05_bf16(const void* qkv, int qkv_strid
                                                   const int* bt, int tw, const int* cu_q, const int* q_start,
                                                   const int* tiles, int n_tiles, int nq, int nkv, int d, int page_size,
                                                   int window, float scale, const int* merges, int n_merges, float* scratch,
-                                                  int pairs, int* err, void* stream) {
+                                                  int pairs, const float* sink, int gate_off, int* err, void* stream) {
   if (n_tiles <= 0) return 0;
-  if (d != A5_D || !err || (n_merges > 0 && (!merges || !scratch || window > 0 || pairs)) || (pairs && window > 0))
+  if (d != A5_D || !err || (n_merges > 0 && (!merges || !scratch || window > 0 || pairs)) || (pairs && window > 0) ||
+      (gate_off >= 0 && gate_off % 8))
     return (int)cudaErrorInvalidValue;
   AttnArgs a;
   int e = fill_args(a, qkv, qkv_stride, out, kp, vp, bt, tw, cu_q, q_start, tiles, nq, nkv, page_size, window, scale);
@@ -593,6 +630,7 @@ Q25_EXPORT int q25_attention_prefill_tcgen05_bf16(const void* qkv, int qkv_strid
   if (((uintptr_t)qkv & 15) || (qkv_stride % 8) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
   cudaError_t ce = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A5_SMEM);
   if (ce != cudaSuccess) return (int)ce;
+  a.sink = sink; a.gate_off = gate_off;                  // sink[h]: a score of the natural exponent, like the scaled scores
   a.part_o = scratch;                                    // [part, kv head, row, D], then [part, kv head, row, (m, l)]
   a.part_ml = scratch ? scratch + (size_t)n_tiles * nkv * A5_ROWS * A5_D : nullptr;
   launch_clusters(pairs ? 2 : 1, attention_prefill_tcgen05_kernel, dim3(n_tiles * nkv * (pairs ? 2 : 1)), dim3(A5_THREADS),

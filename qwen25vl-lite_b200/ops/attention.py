@@ -20,6 +20,7 @@ the device copies back through ``ctx.plan(part)``.
 
 from __future__ import annotations
 
+from collections import OrderedDict
 from typing import Dict, Optional
 
 import numpy as np
@@ -35,6 +36,23 @@ MIN_PAIRS_WALK = 12             # in steps whose longest walk has this many
 MAX_PARTS = 15
 _scratch = {}
 _retired = []
+_plans: "OrderedDict[tuple, Dict[str, np.ndarray]]" = OrderedDict()
+PLANS_KEPT = 16
+
+
+def _remembered(kind: str, args: tuple, host, build) -> Dict[str, np.ndarray]:
+    """The work lists of a step's shape, built once: mixers of one model that differ in what their plans hold ask for
+    the same lists within a step, and prompts cut into portions of one size bring the same shape step after step.
+    The arrays are shared and not to be written to; the dictionary is the caller's."""
+    key = (kind, args, tuple(host.q_lens), tuple(host.starts))
+    lists = _plans.get(key)
+    if lists is None:
+        lists = _plans[key] = build()
+        while len(_plans) > PLANS_KEPT:
+            _plans.popitem(last=False)
+    else:
+        _plans.move_to_end(key)
+    return dict(lists)
 
 
 def plan_step(host, group: int, window: int = 0, places: int = 0) -> Dict[str, np.ndarray]:
@@ -50,6 +68,10 @@ def plan_step(host, group: int, window: int = 0, places: int = 0) -> Dict[str, n
     ``merge128``: the tiles whose parts a second kernel adds up, as (entry, tile, first part, parts);
     ``pairs128`` is not empty when ``tiles128`` is meant for clusters of two CTAs (``pair_split``).
     ``places``: CTAs of the tcgen05 kernel that run at a time for one kv head (0: nothing is cut)."""
+    return _remembered("rows", (group, window, places), host, lambda: _plan_step(host, group, window, places))
+
+
+def _plan_step(host, group: int, window: int, places: int) -> Dict[str, np.ndarray]:
     q_lens, starts = host.q_lens, host.starts
     runs = [i for i, n in enumerate(q_lens) if n > 1 or group > 16]
     run_set = set(runs)
@@ -258,21 +280,40 @@ def paged_attention(ctx, plan, qkv, kv, nq: int, nkv: int, head_dim: int, window
 # ---- attention with a distance bias, a window beside kept first tokens, values of their own size ---------
 
 
+def tcgen05_runs(dk: int, dv: int, group: int, window, keep_first, r1, v_row, softcap, dist_bias) -> bool:
+    """Whether the runs of an attention of this family can go to the tcgen05 prefill kernel: heads of 128 for keys and
+    values alike, every earlier key visible, and nothing between the scaled score and the softmax but a sink."""
+    return (dk == 128 and dv == 128 and group <= 16 and not window and not keep_first and r1 is None and not v_row
+            and not softcap and dist_bias is None)
+
+
 def plan_biased(host, group: int, window: int, keep_first: int) -> Dict[str, np.ndarray]:
     """Work lists of the kernels of ``parts.attention.BiasedWindowAttention`` for a step: the entries
     that bring one token (``decode_items``) and (entry, row tile) pairs of the runs, a tile being
     64 consecutive (token, head of the group) rows; the tiles that walk the most keys go first."""
+    return _remembered("biased", (group, window, keep_first), host, lambda: _plan_biased(host, group, window, keep_first))
+
+
+def _plan_biased(host, group: int, window: int, keep_first: int) -> Dict[str, np.ndarray]:
     q_lens, starts = host.q_lens, host.starts
     singles = [i for i, n in enumerate(q_lens) if n == 1 and group <= 16]     # a warp holds 16 rows: the heads of one token
     runs = [i for i, n in enumerate(q_lens) if n > 1 or group > 16]
-
-    def keys(i, t):                     # keys the tile's last token sees
-        last = starts[i] + min((t * 64 + 63) // group, q_lens[i] - 1)
-        return last + 1 if not window or last < window + keep_first else window + keep_first
-
-    pairs = [(i, t) for i in runs for t in range(-(-q_lens[i] * group // 64))]
-    pairs.sort(key=lambda it: -keys(*it))
-    return {"decode_items": np.asarray(singles, dtype=np.int32), "tiles64": np.asarray(pairs, dtype=np.int32).reshape(-1)}
+    entries, tiles, keys = [], [], []
+    for i in runs:
+        t = np.arange(-(-q_lens[i] * group // 64), dtype=np.int64)
+        last = starts[i] + np.minimum((t * 64 + 63) // group, q_lens[i] - 1)       # the tile's last token: the keys it sees
+        seen = last + 1
+        if window:
+            seen = np.where(last < window + keep_first, seen, window + keep_first)
+        entries.append(np.full(t.shape, i, dtype=np.int64))
+        tiles.append(t)
+        keys.append(seen)
+    if runs:
+        order = np.argsort(-np.concatenate(keys), kind="stable")                    # ties stay in the order of the entries
+        pairs = np.stack([np.concatenate(entries)[order], np.concatenate(tiles)[order]], axis=1)
+    else:
+        pairs = np.zeros((0, 2), dtype=np.int64)
+    return {"decode_items": np.asarray(singles, dtype=np.int32), "tiles64": pairs.astype(np.int32).reshape(-1)}
 
 
 def attend_biased(ctx, plan, qkv, kv, nq: int, nkv: int, dk: int, dv: int, window, keep_first: int, scale: float,
@@ -287,6 +328,19 @@ def attend_biased(ctx, plan, qkv, kv, nq: int, nkv: int, dk: int, dv: int, windo
     window, keep_first = int(window or 0), int(keep_first or 0)
     if kernels.biased_attention_mma_supports(qkv.dtype, dk, dv) and (v_row or dv) % 8 == 0 and (gate_off < 0 or gate_off % 2 == 0):
         items, tiles = plan.get("decode_items"), _pairs(plan.get("tiles64"))
+        tiles128 = _pairs(plan.get("tiles128"), 3)
+        if (tiles128 is not None and tcgen05_runs(dk, dv, nq // nkv, window, keep_first, r1, v_row, softcap, dist_bias)
+                and (gate_off < 0 or gate_off % 8 == 0) and kernels.attention_tcgen05_supports(qkv.dtype, dk, kv.page_size, qkv)):
+            # the runs on the tcgen05 kernel (whose rows take a sink and a gate where they become results); the
+            # single tokens stay with the kernel below
+            merge128 = _pairs(plan.get("merge128"), 4)
+            parts = None if merge128 is None else _scratch_floats(tiles128.shape[0] * nkv * 128 * (dk + 2), qkv.device, "parts")
+            kernels.attention_prefill_tcgen05(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos, tiles128,
+                                              nq, nkv, dk, kv.page_size, 0, scale, merge128, parts, pairs=plan.get("pairs128") is not None,
+                                              sink=sink, gate_off=gate_off)
+            tiles = None
+            if items is None:
+                return out
         splits, scratch = 1, None
         if items is not None:
             visible = min(ctx.max_kv_len, window + keep_first) if window else ctx.max_kv_len

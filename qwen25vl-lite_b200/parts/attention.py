@@ -320,11 +320,25 @@ class SinkAttention(Mixer):
             buckets = log_distance_buckets(rel.shape[0], self.distance_bias[1])
             self.dist_table = rel[torch.tensor(buckets, dtype=torch.long, device=rel.device)].contiguous()
 
+    @property
+    def _tcgen05_runs(self) -> bool:
+        """Whether this mixer's runs of tokens can go to the tcgen05 prefill kernel (bfloat16 permitting)."""
+        return attention_ops.tcgen05_runs(self.head_dim, self.value_dim, self.num_heads // self.num_kv_heads, self.window, 0, None, 0,
+                                          self.softcap, self.distance_bias)
+
     def plan_key(self):
+        if self._tcgen05_runs:
+            return ("sink_attention_tcgen05", self.num_heads // self.num_kv_heads, self.num_kv_heads)
         return ("biased_window_attention", self.num_heads // self.num_kv_heads, self.window or 0, 0)
 
     def plan_step(self, host):
-        return attention_ops.plan_biased(host, self.num_heads // self.num_kv_heads, self.window or 0, 0)
+        group = self.num_heads // self.num_kv_heads
+        plan = attention_ops.plan_biased(host, group, self.window or 0, 0)
+        if self._tcgen05_runs:
+            places = 2 * kernels.sm_count() // self.num_kv_heads           # two CTAs of the tcgen05 kernel fit an SM
+            wide = attention_ops.plan_step(host, group, 0, places)
+            plan.update({name: wide[name] for name in ("tiles128", "merge128", "pairs128")})
+        return plan
 
     def forward(self, ctx, h, stop, residual=None):
         nq, nkv, dk, dv = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim

@@ -135,12 +135,13 @@ def test_queries_tempered_and_keys_and_values_cached(dtype, nq, nkv, dk, dv, wei
 # ---- attention: a distance table, a sink, a gate ----------------------------------------------------------------------------
 
 
-def table_attention_case(dtype, nq, nkv, dk, dv, page_size, entries, seed, peaks, table, sink, gated, scale=0.25):
+def table_attention_case(dtype, nq, nkv, dk, dv, page_size, entries, seed, peaks, table, sink, gated, scale=0.25, places=None):
     """``entries``: (tokens already in the cache, tokens of this step) per request.  ``peaks``: (entry, query token of
     the step, head, key j, strength): that query's score on key j is made to stand out.  ``table``: float64 [L, nq]
     by distance (the last row for every distance beyond), or None.  Pages are handed out in a shuffled order.  The
     step's rows are [queries | keys | values | gates] as a projection leaves them.  Returns the kernels' output beside
-    the float64 reference."""
+    the float64 reference.  ``places``: the step's plan also holds the work lists of the tcgen05 prefill kernel, made for
+    that many CTAs at a time (which decides whether long walks over the keys are cut into parts or halved by pairs)."""
     g = torch.Generator(device=DEV).manual_seed(seed)
     rnd = lambda *shape, scale=1.0: torch.randn(*shape, generator=g, device=DEV) * scale
     group = nq // nkv
@@ -175,7 +176,13 @@ def table_attention_case(dtype, nq, nkv, dk, dv, page_size, entries, seed, peaks
     rows = torch.cat([torch.cat(qs).reshape(n_tokens, nq * dk), filler, gates], dim=1).contiguous()
     ctx = SimpleNamespace(dtype=dtype, token_seq=i32(np.repeat(np.arange(len(entries)), q_lens)), cu_q=i32(np.concatenate([[0], np.cumsum(q_lens)])),
                           q_start_pos=i32(starts), n_seqs=len(entries), n_tokens=n_tokens, max_kv_len=max(total), max_q_len=max(q_lens))
-    plan = {k: (i32(v) if len(v) else None) for k, v in attention_ops.plan_biased(HostStep(q_lens, starts, n_tokens, len(entries)), group, 0, 0).items()}
+    host = HostStep(q_lens, starts, n_tokens, len(entries))
+    lists = attention_ops.plan_biased(host, group, 0, 0)
+    if places is not None:
+        wide = attention_ops.plan_step(host, group, 0, places)
+        lists.update({name: wide[name] for name in ("tiles128", "merge128", "pairs128")})
+    plan = {k: (i32(v) if len(v) else None) for k, v in lists.items()}
+    table_attention_case.last_plan = {k: len(v) for k, v in lists.items()}
     kv = KVStep(k_pages, v_pages, None, blocks.to(DEV), page_size)
     dev_table = None if table is None else torch.tensor(table, dtype=torch.float32, device=DEV).contiguous()
     dev_sink = None if sink is None else torch.tensor(sink, dtype=torch.float32, device=DEV)
@@ -254,6 +261,35 @@ def test_sink_and_gate_beside_the_table(dtype, nq, nkv, dk, dv):
     assert np.abs(no_sink - want).max() > 0.05 and np.abs(no_gate - want).max() > 0.05
     got, want = table_attention_case(*args, None, sink, True)                            # the kind without a table
     assert np.abs(got - want).max() < tol
+
+
+@pytest.mark.parametrize("nq,nkv", [(4, 1), (16, 2), (2, 2)])
+def test_runs_of_heads_of_128_on_the_tcgen05_kernel(nq, nkv):
+    """Without a table, heads of 128 take the tcgen05 prefill kernel for their runs, whose rows add the sink and apply
+    the gate where they become results: whole row tiles, tiles whose keys are cut into parts that a second kernel adds
+    up, and tiles halved by pairs of CTAs; single tokens beside them stay with the other kernel.  Against float64
+    and against the same step on the kernels that every other size takes."""
+    sink = np.linspace(-3.0, 8.0, nq)
+    cases = [([(0, 300), (17, 1), (5, 40), (0, 2)], [(0, 299, 0, 3, 12.0), (0, 130, 1, 64, 12.0), (2, 39, nq - 1, 0, 12.0)], "tiles128"),
+             ([(3000, 128), (40, 1)], [(0, 127, 0, 3, 12.0), (0, 5, 1, 2999, 12.0), (1, 0, nq - 1, 7, 12.0)], "merge128"),
+             ([(1024, 1024)], [(0, 1023, 0, 3, 12.0), (0, 0, 1, 1023, 12.0), (0, 500, nq - 1, 1400, 12.0)], "pairs128")]
+    seen = set()
+    for entries, peaks, _ in cases:
+        args = (torch.bfloat16, nq, nkv, 128, 128, 16, entries, 21, peaks)
+        got, want = table_attention_case(*args, None, sink, True, places=2 * 148 // nkv)
+        used = dict(table_attention_case.last_plan)
+        assert used["tiles128"] > 0
+        seen |= {name for name in ("merge128", "pairs128") if used[name] > 0}
+        assert np.abs(got - want).max() < 3e-2
+        other, _ = table_attention_case(*args, None, sink, True)
+        assert np.abs(got - other).max() < 3e-2
+        _, no_sink = table_attention_case(*args, None, None, True, places=2 * 148 // nkv)
+        _, no_gate = table_attention_case(*args, None, sink, False, places=2 * 148 // nkv)
+        assert np.abs(no_sink - want).max() > 0.01 and np.abs(no_gate - want).max() > 0.05     # among thousands of keys a sink weighs little
+        plain_rows, plain_want = table_attention_case(*args, None, None, False, places=2 * 148 // nkv)     # neither: the kernel as the first model uses it
+        assert np.abs(plain_rows - plain_want).max() < 3e-2
+    if (nq, nkv) == (16, 2):                                 # at these sizes the plan cuts keys both ways
+        assert seen == {"merge128", "pairs128"}, seen
 
 
 # ---- feed-forwards ----------------------------------------------------------------------------------------------------------
