@@ -31,7 +31,7 @@ npy = lambda t: t.detach().double().cpu().numpy()
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("hidden", [96, 100, 2048])
+@pytest.mark.parametrize("hidden", [96, 100, 90, 2048])
 def test_update_normed_into_a_stream_that_is_read_as_it_is(dtype, hidden):
     """x += m * unit(update) * (1 + w), then the sublayer's input is x itself in the activation dtype: through the
     parts (an RMS norm with offset 1 and gain m behind a sublayer, no norm before the next), on all rows, on chosen
