@@ -164,7 +164,16 @@ def _check(code: int, what: str) -> None:
                           f"({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no device'})")
 
 
+# torch's current stream as a raw handle.  ``torch.cuda.current_stream()`` builds a Python object on every call (3.3 us
+# measured, a quarter of a millisecond over the 80 launches of a prompt step); torch's own C entry points hand out the
+# same handle in 0.1 us, and are used where this torch has them.
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_RAW_DEVICE = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> int:
+    if _RAW_STREAM is not None and _RAW_DEVICE is not None:
+        return _RAW_STREAM(_RAW_DEVICE())
     return torch.cuda.current_stream().cuda_stream
 
 
