@@ -30,6 +30,10 @@ struct AttnArgs {
   // multiplies the result (-1: no gate)
   const float* sink;
   int gate_off;
+  // a learned table [dist_rows, nq] added to the scaled score by distance, the last row for every distance beyond
+  // (nullptr: none); only the tcgen05 prefill kernel's build for it reads it
+  const float* dist_bias;
+  int dist_rows;
 };
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -683,6 +687,6 @@ static int fill_args(AttnArgs& a, const void* qkv, int qkv_stride, void* out, co
   a.vpages = (const bf16*)vp; a.block_table = bt; a.table_width = tw; a.cu_q = cu_q; a.q_start_pos = q_start;
   a.items = items; a.nq = nq; a.nkv = nkv; a.page_shift = shift; a.window = window;
   a.scale_log2 = scale * 1.4426950408889634f; a.n_splits = 1; a.part_o = nullptr; a.part_ml = nullptr;
-  a.sink = nullptr; a.gate_off = -1;
+  a.sink = nullptr; a.gate_off = -1; a.dist_bias = nullptr; a.dist_rows = 1;
   return 0;
 }

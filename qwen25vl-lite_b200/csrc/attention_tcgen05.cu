@@ -140,6 +140,11 @@ __device__ __forceinline__ void a5_gate32(float (&v)[32], const bf16* g) {
   }
 }
 
+// TABLE: a build of its own for models whose scores take a bias by distance (AttnArgs.dist_bias), so that the others'
+// kernel carries none of it.  A row whose nearest key of a tile lies at the table's last row or beyond adds that row's
+// number to all its scores of the tile (into the exponent's offset, at no cost per score); in the two or three tiles at
+// the diagonal every score looks its distance up.
+template <bool TABLE>
 __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kernel(AttnArgs a, int n_sms, int* __restrict__ err) {
   constexpr int NROW = A5_NROW, ROWS = A5_ROWS;         // one thread per row; the warp after them issues the products
   constexpr int TMEM_COLS = 256, O_COL = 128;           // two score buffers of 64 columns, then the outputs
@@ -215,6 +220,10 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
   const int tok = live ? R / G : 0, head = live ? R - tok * G : 0;
   const int hi = live ? start + tok : -1;
   const int lo = live ? (a.window > 0 ? max(0, hi - a.window + 1) : 0) : 0;
+  // the row's column of the distance table (scores live in the base-2 domain: entries times log2 e)
+  const float* tab = TABLE ? a.dist_bias + kvh * G + head : nullptr;
+  const int last_dist = TABLE ? a.dist_rows - 1 : 0;
+  const float tab_far = TABLE ? __ldg(tab + (size_t)last_dist * a.nq) * 1.4426950408889634f : 0.f;
 
   // Where the keys lie.  The page lookup is a trip to the L2, so it runs three tiles ahead: the
   // lanes of a warp that stand first look up the rows of the keys that their warp copies (key
@@ -380,6 +389,19 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
           s[j] = (kidx >= lo && kidx <= hi) ? s[j] : -INFINITY;
         }
       }
+      float sc = a.scale_log2, add = 0.f;                  // a score enters the exponent as s * sc + add
+      if (TABLE) {
+        if (hi - (key0 + A5_BN - 1) >= last_dist) {
+          add = tab_far;
+        } else {
+#pragma unroll
+          for (int j = 0; j < A5_BN; ++j) {
+            const int dist = min(max(hi - (key0 + j), 0), last_dist);
+            s[j] = fmaf(s[j], a.scale_log2, __ldg(tab + (size_t)dist * a.nq) * 1.4426950408889634f);
+          }
+          sc = 1.0f;
+        }
+      }
       float mx0 = a5_max3(s[0], s[1], s[2]), mx1 = a5_max3(s[3], s[4], s[5]);   // two chains of three-input maxima
 #pragma unroll
       for (int j = 6; j + 3 < A5_BN; j += 4) {
@@ -387,7 +409,7 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
         mx1 = a5_max3(mx1, s[j + 2], s[j + 3]);
       }
       float mx = a5_max3(mx0, mx1, fmaxf(s[A5_BN - 2], s[A5_BN - 1]));
-      mx *= a.scale_log2;                                  // the scale is positive: the maximum of the scaled scores
+      mx = fmaf(mx, sc, add);                              // the scale is positive: the maximum of the scaled scores
       const bool grow = mx > m_used + 8.0f || (m_used == -INFINITY && mx != -INFINITY);
       if (__any_sync(0xffffffffu, grow)) {
         const float factor = grow ? (m_used == -INFINITY ? 0.f : a5_ex2(m_used - mx)) : 1.0f;
@@ -409,13 +431,13 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attention_prefill_tcgen05_kerne
           }
         }
       }
-      const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+      const float neg_m = (m_used == -INFINITY ? 0.f : -m_used) + add;
       float sum = 0.f;
       unsigned w[A5_BN / 2];
 #pragma unroll
       for (int e = 0; e < A5_BN / 2; ++e) {
-        const float p0 = a5_ex2(fmaf(s[2 * e], a.scale_log2, neg_m));
-        const float p1 = a5_ex2(fmaf(s[2 * e + 1], a.scale_log2, neg_m));
+        const float p0 = a5_ex2(fmaf(s[2 * e], sc, neg_m));
+        const float p1 = a5_ex2(fmaf(s[2 * e + 1], sc, neg_m));
         sum += p0 + p1;
         w[e] = pack_bf16(p0, p1);
       }
@@ -619,21 +641,24 @@ Q25_EXPORT int q25_attention_prefill_tcgen05_bf16(const void* qkv, int qkv_strid
                                                   const int* bt, int tw, const int* cu_q, const int* q_start,
                                                   const int* tiles, int n_tiles, int nq, int nkv, int d, int page_size,
                                                   int window, float scale, const int* merges, int n_merges, float* scratch,
-                                                  int pairs, const float* sink, int gate_off, int* err, void* stream) {
+                                                  int pairs, const float* sink, int gate_off, const float* dist_bias, int dist_rows,
+                                                  int* err, void* stream) {
   if (n_tiles <= 0) return 0;
   if (d != A5_D || !err || (n_merges > 0 && (!merges || !scratch || window > 0 || pairs)) || (pairs && window > 0) ||
-      (gate_off >= 0 && gate_off % 8))
+      (gate_off >= 0 && gate_off % 8) || (dist_bias && dist_rows < 1))
     return (int)cudaErrorInvalidValue;
   AttnArgs a;
   int e = fill_args(a, qkv, qkv_stride, out, kp, vp, bt, tw, cu_q, q_start, tiles, nq, nkv, page_size, window, scale);
   if (e) return e;
   if (((uintptr_t)qkv & 15) || (qkv_stride % 8) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
-  cudaError_t ce = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A5_SMEM);
+  void (*kernel)(AttnArgs, int, int*) = dist_bias ? attention_prefill_tcgen05_kernel<true> : attention_prefill_tcgen05_kernel<false>;
+  cudaError_t ce = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A5_SMEM);
   if (ce != cudaSuccess) return (int)ce;
+  a.dist_bias = dist_bias; a.dist_rows = dist_bias ? dist_rows : 1;
   a.sink = sink; a.gate_off = gate_off;                  // sink[h]: a score of the natural exponent, like the scaled scores
   a.part_o = scratch;                                    // [part, kv head, row, D], then [part, kv head, row, (m, l)]
   a.part_ml = scratch ? scratch + (size_t)n_tiles * nkv * A5_ROWS * A5_D : nullptr;
-  launch_clusters(pairs ? 2 : 1, attention_prefill_tcgen05_kernel, dim3(n_tiles * nkv * (pairs ? 2 : 1)), dim3(A5_THREADS),
+  launch_clusters(pairs ? 2 : 1, kernel, dim3(n_tiles * nkv * (pairs ? 2 : 1)), dim3(A5_THREADS),
                   (size_t)A5_SMEM, (cudaStream_t)stream, a, device_sm_count(), err);
   if (n_merges > 0)
     launch(attention_prefill_merge_kernel, dim3(n_merges * nkv * (A5_ROWS / A5_MERGE_WARPS)), dim3(A5_MERGE_WARPS * 32), 0,

@@ -280,11 +280,12 @@ def paged_attention(ctx, plan, qkv, kv, nq: int, nkv: int, head_dim: int, window
 # ---- attention with a distance bias, a window beside kept first tokens, values of their own size ---------
 
 
-def tcgen05_runs(dk: int, dv: int, group: int, window, keep_first, r1, v_row, softcap, dist_bias) -> bool:
+def tcgen05_runs(dk: int, dv: int, group: int, window, keep_first, r1, v_row, softcap) -> bool:
     """Whether the runs of an attention of this family can go to the tcgen05 prefill kernel: heads of 128 for keys and
-    values alike, every earlier key visible, and nothing between the scaled score and the softmax but a sink."""
+    values alike, every earlier key visible, and nothing between the scaled score and the softmax but a table by
+    distance and a sink."""
     return (dk == 128 and dv == 128 and group <= 16 and not window and not keep_first and r1 is None and not v_row
-            and not softcap and dist_bias is None)
+            and not softcap)
 
 
 def plan_biased(host, group: int, window: int, keep_first: int) -> Dict[str, np.ndarray]:
@@ -329,15 +330,15 @@ def attend_biased(ctx, plan, qkv, kv, nq: int, nkv: int, dk: int, dv: int, windo
     if kernels.biased_attention_mma_supports(qkv.dtype, dk, dv) and (v_row or dv) % 8 == 0 and (gate_off < 0 or gate_off % 2 == 0):
         items, tiles = plan.get("decode_items"), _pairs(plan.get("tiles64"))
         tiles128 = _pairs(plan.get("tiles128"), 3)
-        if (tiles128 is not None and tcgen05_runs(dk, dv, nq // nkv, window, keep_first, r1, v_row, softcap, dist_bias)
+        if (tiles128 is not None and tcgen05_runs(dk, dv, nq // nkv, window, keep_first, r1, v_row, softcap)
                 and (gate_off < 0 or gate_off % 8 == 0) and kernels.attention_tcgen05_supports(qkv.dtype, dk, kv.page_size, qkv)):
-            # the runs on the tcgen05 kernel (whose rows take a sink and a gate where they become results); the
-            # single tokens stay with the kernel below
+            # the runs on the tcgen05 kernel (whose rows take a table by distance in their scores, and a sink and a gate
+            # where they become results); the single tokens stay with the kernel below
             merge128 = _pairs(plan.get("merge128"), 4)
             parts = None if merge128 is None else _scratch_floats(tiles128.shape[0] * nkv * 128 * (dk + 2), qkv.device, "parts")
             kernels.attention_prefill_tcgen05(qkv, out, kv.k_pages, kv.v_pages, kv.block_table, ctx.cu_q, ctx.q_start_pos, tiles128,
                                               nq, nkv, dk, kv.page_size, 0, scale, merge128, parts, pairs=plan.get("pairs128") is not None,
-                                              sink=sink, gate_off=gate_off)
+                                              sink=sink, gate_off=gate_off, dist_bias=dist_bias)
             tiles = None
             if items is None:
                 return out

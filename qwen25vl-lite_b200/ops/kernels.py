@@ -373,7 +373,8 @@ def attention_prefill_tcgen05(qkv: torch.Tensor, out: torch.Tensor, k_pages: tor
                               tiles: torch.Tensor, nq: int, nkv: int, head_dim: int, page_size: int, window: int,
                               scale: float, merges: Optional[torch.Tensor] = None,
                               scratch: Optional[torch.Tensor] = None, pairs: bool = False,
-                              sink: Optional[torch.Tensor] = None, gate_off: int = -1) -> None:
+                              sink: Optional[torch.Tensor] = None, gate_off: int = -1,
+                              dist_bias: Optional[torch.Tensor] = None) -> None:
     """``attention_prefill`` on the tcgen05 tensor cores (scores, P and the outputs in tensor memory).
     ``tiles`` is int32 [n, 3]: (entry, row tile, code) with row tiles of 128 rows; code 1 is a whole
     tile, else first part << 8 | part << 4 | parts: one of the parts its keys are cut into, which
@@ -382,9 +383,11 @@ def attention_prefill_tcgen05(qkv: torch.Tensor, out: torch.Tensor, k_pages: tor
     kernel adds up.  ``pairs``: every piece of work goes to a cluster of two CTAs instead; code 2 then
     means half of the keys for each, added up through the cluster's shared memory, code 1 the whole
     tile for one of them.  ``sink`` (float32 [nq]) joins each head's denominator; ``gate_off`` >= 0 (a multiple of 8):
-    the rows of ``qkv`` hold nq * head_dim gate channels there, whose sigmoid multiplies the result."""
+    the rows of ``qkv`` hold nq * head_dim gate channels there, whose sigmoid multiplies the result.  ``dist_bias``
+    (float32 [rows, nq]): ``dist_bias[min(i - j, rows - 1), head]`` is added to the scaled score."""
     if sink is not None:
         _dev(sink, torch.float32, "attention sink")
+    _check_dist_bias(dist_bias, nq)
     if gate_off >= 0 and gate_off % 8:
         raise KernelError("attention_prefill_tcgen05: the gate channels must start on a 16-byte boundary")
     if not attention_tcgen05_supports(qkv.dtype, head_dim, page_size, qkv):
@@ -398,11 +401,12 @@ def attention_prefill_tcgen05(qkv: torch.Tensor, out: torch.Tensor, k_pages: tor
     if pairs and window:
         raise KernelError("attention_prefill_tcgen05: keys behind a window are not cut")
     _check(_fn("q25_attention_prefill_tcgen05_bf16",
-               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _I, _P, _I, _P, _I, _P, _P])(
+               [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P])(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], cu_q.data_ptr(), q_start_pos.data_ptr(), tiles.data_ptr(), tiles.shape[0], nq, nkv,
         head_dim, page_size, int(window or 0), float(scale), _ptr(merges), n_merge, _ptr(scratch), int(bool(pairs)),
-        _ptr(sink), int(gate_off), error_flag(qkv.device).data_ptr(), _stream()), "attention_prefill_tcgen05")
+        _ptr(sink), int(gate_off), _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0],
+        error_flag(qkv.device).data_ptr(), _stream()), "attention_prefill_tcgen05")
     if n_merge:
         count_replayed(1)                      # the merge kernel, launched by the same call
 

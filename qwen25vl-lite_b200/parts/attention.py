@@ -324,7 +324,7 @@ class SinkAttention(Mixer):
     def _tcgen05_runs(self) -> bool:
         """Whether this mixer's runs of tokens can go to the tcgen05 prefill kernel (bfloat16 permitting)."""
         return attention_ops.tcgen05_runs(self.head_dim, self.value_dim, self.num_heads // self.num_kv_heads, self.window, 0, None, 0,
-                                          self.softcap, self.distance_bias)
+                                          self.softcap)
 
     def plan_key(self):
         if self._tcgen05_runs:

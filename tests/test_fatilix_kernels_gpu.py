@@ -265,8 +265,8 @@ def test_sink_and_gate_beside_the_table(dtype, nq, nkv, dk, dv):
 
 @pytest.mark.parametrize("nq,nkv", [(4, 1), (16, 2), (2, 2)])
 def test_runs_of_heads_of_128_on_the_tcgen05_kernel(nq, nkv):
-    """Without a table, heads of 128 take the tcgen05 prefill kernel for their runs, whose rows add the sink and apply
-    the gate where they become results: whole row tiles, tiles whose keys are cut into parts that a second kernel adds
+    """Heads of 128 take the tcgen05 prefill kernel for their runs, whose rows add the table to their scores, and add the
+    sink and apply the gate where they become results: whole row tiles, tiles whose keys are cut into parts that a second kernel adds
     up, and tiles halved by pairs of CTAs; single tokens beside them stay with the other kernel.  Against float64
     and against the same step on the kernels that every other size takes."""
     sink = np.linspace(-3.0, 8.0, nq)
@@ -290,6 +290,22 @@ def test_runs_of_heads_of_128_on_the_tcgen05_kernel(nq, nkv):
         assert np.abs(plain_rows - plain_want).max() < 3e-2
     if (nq, nkv) == (16, 2):                                 # at these sizes the plan cuts keys both ways
         assert seen == {"merge128", "pairs128"}, seen
+    # with a table of 12 rows that ends at distance 40: tiles at the diagonal look every distance up, the others add one number
+    table, _ = distinct_table(12, 40.0, nq, 5)
+    L = len(table)
+    for entries, peaks, _ in cases:
+        (s0, n0) = entries[0]
+        peaks = peaks + [(0, n0 - 1, 0, s0 + n0 - 1 - (L - 2), 12.0), (0, n0 - 2, 1, s0 + n0 - 2 - (L - 1), 12.0), (0, n0 - 3, nq - 1, s0 + n0 - 3 - L, 12.0)]
+        args = (torch.bfloat16, nq, nkv, 128, 128, 16, entries, 22, peaks)
+        got, want = table_attention_case(*args, table, sink, True, places=2 * 148 // nkv)
+        assert np.abs(got - want).max() < 3e-2
+        other, _ = table_attention_case(*args, table, sink, True)
+        assert np.abs(got - other).max() < 3e-2
+        shifted = np.concatenate([table[:1], table[:-1]])
+        cut = np.concatenate([table, np.zeros((1, nq))])
+        for wrong in (shifted, cut, None):
+            _, off = table_attention_case(*args, wrong, sink, True, places=2 * 148 // nkv)
+            assert np.abs(off - want).max() > 0.02
 
 
 # ---- feed-forwards ----------------------------------------------------------------------------------------------------------
